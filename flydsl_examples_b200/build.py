@@ -1,0 +1,73 @@
+"""Ahead-of-time build of libb200_gemm.so (sm_100a only) with nvcc.
+
+Replaces the reference's in-process JIT (`flyc.compile` through kernels/common.py:7-39): there is no
+run-time compilation here, the shared library is built once and kept in-tree next to this file.
+
+    python -m flydsl_examples_b200.build [--force] [--verbose]
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+CSRC = PKG_DIR / "csrc"
+INCLUDE = PKG_DIR.parent / "include"
+LIB_PATH = PKG_DIR / "libb200_gemm.so"
+STAMP_PATH = PKG_DIR / "libb200_gemm.so.stamp"
+
+SOURCES = [CSRC / "gemm_api.cu"]
+HEADERS = [CSRC / "gemm_kernel.cuh", CSRC / "ptx.cuh", INCLUDE / "b200_gemm.h"]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-shared", "-Xcompiler", "-fPIC",
+    "--expt-relaxed-constexpr",
+]
+
+
+def _nvcc() -> str:
+    cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(cand).exists():
+        raise RuntimeError("nvcc not found; set NVCC or put /usr/local/cuda/bin on PATH")
+    return cand
+
+
+def _source_digest() -> str:
+    h = hashlib.sha256()
+    for f in SOURCES + HEADERS:
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def is_current() -> bool:
+    return LIB_PATH.exists() and STAMP_PATH.exists() and STAMP_PATH.read_text().strip() == _source_digest()
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile the library if the sources changed since the last build; return its path."""
+    if not force and is_current():
+        return LIB_PATH
+    cmd = [_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}"]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    cmd += ["-o", str(LIB_PATH), *map(str, SOURCES)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose:
+        sys.stderr.write(proc.stderr)
+    if proc.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
+    STAMP_PATH.write_text(_source_digest() + "\n")
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    print(path)

@@ -1,0 +1,383 @@
+// Host side of libb200_gemm.so: argument validation, plan resolution, TMA tensor-map encoding, variant table
+// and launch. Exports the C ABI declared in include/b200_gemm.h. No torch types; no device allocation; no sync.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/b200_gemm.h"
+#include "gemm_kernel.cuh"
+
+namespace b200 {
+
+constexpr int kSmemLimit = 232448;  // 227 KB opt-in dynamic shared memory per CTA on sm_100
+constexpr int kMaxDevices = 16;
+
+// ------------------------------------------------------------------ driver entry point (no -lcuda link needed)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+static thread_local char g_last_cuda_error[256] = "";
+
+// ------------------------------------------------------------------ variant table
+typedef void (*KernelFn)(const GemmParams);
+struct Variant {
+  int tile_q, cta_group, max_stages;
+  KernelFn fn[13];  // indexed by stage count (2..12)
+};
+
+template <int TILE_Q, int S>
+constexpr KernelFn kfn() {
+  if constexpr (SmemLayout<TILE_Q, S>::kDynBytes <= kSmemLimit)
+    return gemm_a16w16_sm100_kernel<TILE_Q, S>;
+  else
+    return nullptr;
+}
+
+#define B200_VARIANT(TQ, MAXS)                                                                                    \
+  {                                                                                                               \
+    TQ, 1, MAXS, {                                                                                                \
+      nullptr, nullptr, kfn<TQ, 2>(), kfn<TQ, 3>(), kfn<TQ, 4>(), kfn<TQ, 5>(), kfn<TQ, 6>(), nullptr,            \
+          kfn<TQ, 8>(), nullptr, kfn<TQ, 10>(), nullptr, nullptr                                                  \
+    }                                                                                                             \
+  }
+
+static const Variant kVariants[] = {
+    B200_VARIANT(16, 10), B200_VARIANT(32, 10), B200_VARIANT(64, 8), B200_VARIANT(128, 6), B200_VARIANT(256, 4),
+};
+constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
+
+static const Variant* find_variant(int tile_q, int cta_group) {
+  for (int i = 0; i < kNumVariants; ++i)
+    if (kVariants[i].tile_q == tile_q && kVariants[i].cta_group == cta_group) return &kVariants[i];
+  return nullptr;
+}
+
+static int dyn_smem_bytes(int tile_q, int stages) {
+  return stages * (kUStageBytes + tile_q * kTileK * 2) + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024;
+}
+
+struct DeviceInfo {
+  int sm_count = 0;
+  bool attr_set[kNumVariants][13] = {};
+};
+static DeviceInfo g_dev[kMaxDevices];
+static std::mutex g_dev_mutex;
+
+static int current_device_info(DeviceInfo** out, int* dev_out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_GEMM_ERR_LAUNCH;
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  DeviceInfo& d = g_dev[dev];
+  if (d.sm_count == 0) {
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || d.sm_count <= 0)
+      return B200_GEMM_ERR_LAUNCH;
+  }
+  *out = &d;
+  *dev_out = dev;
+  return 0;
+}
+
+// ------------------------------------------------------------------ plan
+static inline uint64_t round_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
+
+static bool tma_encodable(const void* ptr, int64_t ld) {
+  return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && ((ld * 2) & 15) == 0;
+}
+
+struct Resolved {
+  b200_gemm_plan plan;
+  // operand roles after swap
+  const void* u_ptr;
+  const void* v_ptr;
+  int64_t u_ld, v_ld;
+  int u_mn, v_mn;  // 1 = MN-major (P/Q contiguous)
+  int P, Q;
+  uint64_t off_partials, off_repack_a, off_repack_b;
+  int64_t ra_ld, rb_ld;  // pitches of the repacked images
+};
+
+static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int sm_count_hint) {
+  if (a == nullptr) return B200_GEMM_ERR_BAD_ARG;
+  if (a->m <= 0 || a->n <= 0 || a->k <= 0) return B200_GEMM_ERR_BAD_ARG;
+  if (a->m > 0x7fffffffLL || a->n > 0x7fffffffLL || a->k > 0x7fffffffLL) return B200_GEMM_ERR_TOO_LARGE;
+  if (a->in_dtype != B200_GEMM_DTYPE_BF16 && a->in_dtype != B200_GEMM_DTYPE_FP16) return B200_GEMM_ERR_BAD_ARG;
+  if (a->out_dtype != a->in_dtype && a->out_dtype != B200_GEMM_DTYPE_FP32) return B200_GEMM_ERR_BAD_ARG;
+  const int64_t a_min_ld = a->a_trans ? a->m : a->k;
+  const int64_t b_min_ld = a->b_trans ? a->k : a->n;
+  if (a->lda < a_min_ld || a->ldb < b_min_ld || a->ldo < a->n) return B200_GEMM_ERR_BAD_ARG;
+
+  const b200_gemm_policy& pol = a->policy;
+  b200_gemm_plan& pl = r->plan;
+  memset(&pl, 0, sizeof(pl));
+  pl.cta_group = pol.cta_group == 0 ? 1 : pol.cta_group;
+  pl.swap_ab = pol.swap_ab ? 1 : 0;
+  pl.tile_m = kTileP * pl.cta_group;
+  pl.tile_n = pol.tile_n;
+  pl.tile_k = kTileK;
+  pl.group_m = pol.group_m < 0 ? 0 : pol.group_m;
+  const Variant* var = find_variant(pl.tile_n, pl.cta_group);
+  if (var == nullptr) return B200_GEMM_ERR_BAD_POLICY;
+
+  // A is K-major when 'n'; B[K,N] is K-major when 't'.
+  const int a_mn = a->a_trans ? 1 : 0;
+  const int b_mn = a->b_trans ? 0 : 1;
+  pl.a_repacked = tma_encodable(a->a, a->lda) ? 0 : 1;
+  pl.b_repacked = tma_encodable(a->b, a->ldb) ? 0 : 1;
+  // Repacked images: K-major operand -> [rows, round_up(K,8)]; MN-major operand -> [K, round_up(rows,8)].
+  const int64_t a_rows = a_mn ? a->k : a->m, a_cols = a_mn ? a->m : a->k;
+  const int64_t b_rows = b_mn ? a->k : a->n, b_cols = b_mn ? a->n : a->k;
+  r->ra_ld = (int64_t)round_up(a_cols, 8);
+  r->rb_ld = (int64_t)round_up(b_cols, 8);
+
+  if (!pl.swap_ab) {
+    r->P = (int)a->m, r->Q = (int)a->n;
+    r->u_mn = a_mn, r->v_mn = b_mn;
+  } else {
+    r->P = (int)a->n, r->Q = (int)a->m;
+    r->u_mn = b_mn, r->v_mn = a_mn;
+  }
+  if (r->v_mn && pl.tile_n < 64) return B200_GEMM_ERR_BAD_POLICY;  // an MN-major box is 64 elements wide
+
+  pl.tiles_p = (r->P + pl.tile_m - 1) / pl.tile_m;
+  pl.tiles_q = (r->Q + pl.tile_n - 1) / pl.tile_n;
+  const int64_t tiles = (int64_t)pl.tiles_p * pl.tiles_q;
+  const int kb_total = (int)((a->k + kTileK - 1) / kTileK);
+  pl.split_k = pol.split_k <= 0 ? 1 : pol.split_k;
+  if (pl.split_k > kb_total) pl.split_k = kb_total;  // never an empty slice
+  if (tiles * pl.split_k > 0x7fffffffLL) return B200_GEMM_ERR_TOO_LARGE;
+  pl.num_units = (int)(tiles * pl.split_k);
+
+  int stages = pol.stages;
+  if (stages <= 0 || stages > var->max_stages) stages = var->max_stages;
+  while (stages >= 2 && (var->fn[stages] == nullptr)) --stages;
+  if (stages < 2) return B200_GEMM_ERR_BAD_POLICY;
+  pl.stages = stages;
+  pl.smem_bytes = dyn_smem_bytes(pl.tile_n, stages);
+  pl.tmem_cols = 2 * pl.tile_n < 32 ? 32 : 2 * pl.tile_n;
+
+  int sms = sm_count_hint;
+  if (need_sm_count && sms <= 0) return B200_GEMM_ERR_LAUNCH;
+  if (sms <= 0) sms = 148;
+  int cap = pol.max_ctas > 0 ? pol.max_ctas : sms;
+  pl.grid = pl.num_units < cap ? pl.num_units : cap;
+
+  pl.counter_bytes = pl.split_k > 1 ? round_up((uint64_t)tiles * 4, 256) : 0;
+  pl.partial_bytes = pl.split_k > 1 ? (uint64_t)pl.num_units * kTileP * pl.tile_n * 4 : 0;
+  const uint64_t ra = pl.a_repacked ? round_up((uint64_t)a_rows * r->ra_ld * 2, 256) : 0;
+  const uint64_t rb = pl.b_repacked ? round_up((uint64_t)b_rows * r->rb_ld * 2, 256) : 0;
+  pl.repack_bytes = ra + rb;
+  r->off_partials = pl.counter_bytes;
+  r->off_repack_a = r->off_partials + pl.partial_bytes;
+  r->off_repack_b = r->off_repack_a + ra;
+  pl.workspace_bytes = r->off_repack_b + rb;
+  return 0;
+}
+
+// ------------------------------------------------------------------ tensor maps
+// K-major operand [rows, K] (K contiguous): dims {K, rows}, box {64, box_rows}.
+// MN-major operand [K, rows] (rows contiguous): dims {rows, K}, box {64, 64}.
+static int encode_operand(CUtensorMap* map, const void* ptr, int in_dtype, int mn_major, int64_t rows, int64_t k,
+                          int64_t ld, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return B200_GEMM_ERR_DRIVER;
+  const CUtensorMapDataType dt = in_dtype == B200_GEMM_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t dims[2], strides[1];
+  cuuint32_t box[2], estr[2] = {1, 1};
+  if (!mn_major) {
+    dims[0] = (cuuint64_t)k, dims[1] = (cuuint64_t)rows;
+    box[0] = kTileK, box[1] = (cuuint32_t)box_rows;
+  } else {
+    dims[0] = (cuuint64_t)rows, dims[1] = (cuuint64_t)k;
+    box[0] = 64, box[1] = kTileK;
+  }
+  strides[0] = (cuuint64_t)ld * 2;
+  const CUresult res = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return res == CUDA_SUCCESS ? 0 : B200_GEMM_ERR_TENSOR_MAP;
+}
+
+// smem matrix descriptor template (everything but the start address) for a 128-byte-swizzled operand stage.
+//   bits 16-29 leading byte offset >> 4, 32-45 stride byte offset >> 4, 46-47 version (1), 61-63 layout (2 = SW128).
+// K-major: rows are 128 B apart, 8-row groups 1024 B apart (SBO); LBO unused (1). K=16 step = 32 B.
+// MN-major: each 64-element box is [64 K rows x 128 B]; 8-K-row groups 1024 B apart (SBO), boxes 8192 B apart (LBO);
+//           K=16 step = 2048 B.
+static void make_desc(int mn_major, uint32_t* hi, uint32_t* lo, uint32_t* kstep) {
+  const uint32_t sbo = 1024 >> 4;
+  const uint32_t lbo = mn_major ? (8192 >> 4) : 1;
+  *lo = lbo << 16;
+  *hi = sbo | (1u << 14) | (2u << 29);
+  *kstep = mn_major ? (2048 >> 4) : (32 >> 4);
+}
+
+static uint32_t make_idesc(int in_dtype, int u_mn, int v_mn, int mma_m, int mma_n) {
+  const uint32_t fmt = in_dtype == B200_GEMM_DTYPE_BF16 ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(u_mn) << 15) | (uint32_t(v_mn) << 16) | (uint32_t(mma_n >> 3) << 17) |
+         (uint32_t(mma_m >> 4) << 24);
+}
+
+static int set_cuda_error(cudaError_t e) {
+  snprintf(g_last_cuda_error, sizeof(g_last_cuda_error), "%s", cudaGetErrorString(e));
+  return B200_GEMM_ERR_LAUNCH;
+}
+
+static int launch(const b200_gemm_args* a, cudaStream_t stream) {
+  DeviceInfo* dev = nullptr;
+  int dev_id = 0;
+  int rc = current_device_info(&dev, &dev_id);
+  if (rc) return rc;
+  Resolved r;
+  rc = resolve(a, &r, true, dev->sm_count);
+  if (rc) return rc;
+  const b200_gemm_plan& pl = r.plan;
+  if (a->a == nullptr || a->b == nullptr || a->out == nullptr) return B200_GEMM_ERR_BAD_ARG;
+  if (pl.workspace_bytes > 0 && (a->workspace == nullptr || a->workspace_bytes < pl.workspace_bytes ||
+                                 (reinterpret_cast<uintptr_t>(a->workspace) & 255) != 0))
+    return B200_GEMM_ERR_WORKSPACE;
+  uint8_t* ws = reinterpret_cast<uint8_t*>(a->workspace);
+
+  // Operands TMA cannot describe are first copied into an aligned image (same stream, ordered before the GEMM).
+  const void* pa = a->a;
+  const void* pb = a->b;
+  int64_t lda = a->lda, ldb = a->ldb;
+  const int a_mn = a->a_trans ? 1 : 0, b_mn = a->b_trans ? 0 : 1;
+  if (pl.a_repacked) {
+    const int rows = (int)(a_mn ? a->k : a->m), cols = (int)(a_mn ? a->m : a->k);
+    uint16_t* dst = reinterpret_cast<uint16_t*>(ws + r.off_repack_a);
+    const long long total = (long long)rows * ((cols + 7) / 8);
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    repack_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint16_t*>(a->a), a->lda, dst, r.ra_ld, rows, cols);
+    pa = dst, lda = r.ra_ld;
+  }
+  if (pl.b_repacked) {
+    const int rows = (int)(b_mn ? a->k : a->n), cols = (int)(b_mn ? a->n : a->k);
+    uint16_t* dst = reinterpret_cast<uint16_t*>(ws + r.off_repack_b);
+    const long long total = (long long)rows * ((cols + 7) / 8);
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    repack_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint16_t*>(a->b), a->ldb, dst, r.rb_ld, rows, cols);
+    pb = dst, ldb = r.rb_ld;
+  }
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const void* u_ptr = pl.swap_ab ? pb : pa;
+  const void* v_ptr = pl.swap_ab ? pa : pb;
+  const int64_t u_ld = pl.swap_ab ? ldb : lda, v_ld = pl.swap_ab ? lda : ldb;
+  rc = encode_operand(&p.tmap_u, u_ptr, a->in_dtype, r.u_mn, r.P, a->k, u_ld, kTileP);
+  if (rc) return rc;
+  rc = encode_operand(&p.tmap_v, v_ptr, a->in_dtype, r.v_mn, r.Q, a->k, v_ld, pl.tile_n);
+  if (rc) return rc;
+  p.out = a->out;
+  p.bias = a->bias;
+  p.tickets = reinterpret_cast<int*>(ws);
+  p.partials = reinterpret_cast<float*>(ws + r.off_partials);
+  p.status = a->status;
+  p.ldo = a->ldo;
+  p.P = r.P, p.Q = r.Q, p.K = (int)a->k;
+  p.tiles_p = pl.tiles_p, p.tiles_q = pl.tiles_q, p.num_tiles = pl.tiles_p * pl.tiles_q;
+  p.kb_total = (int)((a->k + kTileK - 1) / kTileK);
+  p.split_k = pl.split_k;
+  p.num_units = pl.num_units;
+  p.group_p = pl.group_m;
+  p.swap_out = pl.swap_ab;
+  p.out_dtype = a->out_dtype;
+  p.in_dtype = a->in_dtype;
+  p.u_mn_major = r.u_mn, p.v_mn_major = r.v_mn;
+  p.idesc = make_idesc(a->in_dtype, r.u_mn, r.v_mn, kTileP, pl.tile_n);
+  make_desc(r.u_mn, &p.u_desc_hi, &p.u_desc_lo, &p.u_kstep);
+  make_desc(r.v_mn, &p.v_desc_hi, &p.v_desc_lo, &p.v_kstep);
+
+  const Variant* var = find_variant(pl.tile_n, pl.cta_group);
+  const int vi = (int)(var - kVariants);
+  KernelFn fn = var->fn[pl.stages];
+  {
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    if (!dev->attr_set[vi][pl.stages]) {
+      cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes);
+      if (e != cudaSuccess) return set_cuda_error(e);
+      dev->attr_set[vi][pl.stages] = true;
+    }
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(pl.grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.stream = stream;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, fn, p);
+  if (e != cudaSuccess) return set_cuda_error(e);
+  return 0;
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int b200_gemm_a16w16(const b200_gemm_args* args, void* cuda_stream) {
+  return b200::launch(args, reinterpret_cast<cudaStream_t>(cuda_stream));
+}
+
+int b200_gemm_plan_query(const b200_gemm_args* args, b200_gemm_plan* plan) {
+  if (plan == nullptr) return B200_GEMM_ERR_BAD_ARG;
+  b200::Resolved r;
+  int sms = 0;
+  {
+    b200::DeviceInfo* dev = nullptr;
+    int dev_id = 0;
+    if (b200::current_device_info(&dev, &dev_id) == 0) sms = dev->sm_count;
+  }
+  const int rc = b200::resolve(args, &r, false, sms);
+  if (rc) return rc;
+  *plan = r.plan;
+  return 0;
+}
+
+uint64_t b200_gemm_workspace_bytes(const b200_gemm_args* args) {
+  b200_gemm_plan plan;
+  if (b200_gemm_plan_query(args, &plan) != 0) return 0;
+  return plan.workspace_bytes;
+}
+
+int b200_gemm_num_variants(void) { return b200::kNumVariants; }
+
+int b200_gemm_describe_variant(int index, int32_t* tile_n, int32_t* cta_group, int32_t* max_stages) {
+  if (index < 0 || index >= b200::kNumVariants) return B200_GEMM_ERR_BAD_ARG;
+  if (tile_n) *tile_n = b200::kVariants[index].tile_q;
+  if (cta_group) *cta_group = b200::kVariants[index].cta_group;
+  if (max_stages) *max_stages = b200::kVariants[index].max_stages;
+  return 0;
+}
+
+const char* b200_gemm_strerror(int code) {
+  switch (code) {
+    case B200_GEMM_OK: return "ok";
+    case B200_GEMM_ERR_BAD_ARG: return "bad argument (null pointer, size, stride or dtype)";
+    case B200_GEMM_ERR_BAD_POLICY: return "unsupported policy (tile_n / cta_group / stages / layout combination)";
+    case B200_GEMM_ERR_WORKSPACE: return "workspace missing, misaligned (256 B) or smaller than b200_gemm_workspace_bytes()";
+    case B200_GEMM_ERR_TENSOR_MAP: return "cuTensorMapEncodeTiled rejected an operand";
+    case B200_GEMM_ERR_LAUNCH: return b200::g_last_cuda_error[0] ? b200::g_last_cuda_error : "CUDA runtime error";
+    case B200_GEMM_ERR_DRIVER: return "cuTensorMapEncodeTiled driver entry point not available";
+    case B200_GEMM_ERR_TOO_LARGE: return "size beyond a fixed limit of this entry point";
+    default: return "unknown error code";
+  }
+}
+
+const char* b200_gemm_version(void) { return "b200_gemm 0.1 sm_100a"; }
+
+}  // extern "C"

@@ -1,0 +1,467 @@
+// Persistent, warp-specialised A16W16 GEMM for sm_100a.
+//
+//   D[P,Q] = U[P,K] * V[Q,K]^T        U = the operand that sits on the 128-row MMA axis (TMEM lanes)
+//                                      V = the operand that sits on the MMA N axis (TMEM columns)
+// The host maps (A,B) -> (U,V) normally and (B,A) -> (U,V) for swap_ab; the epilogue then writes D or D^T.
+// Either operand may be K-contiguous ("K-major") or P/Q-contiguous ("MN-major"): that only changes how the
+// host encodes the tensor map, how many 64-wide TMA boxes one stage takes, and two descriptor fields.
+//
+// Roles (192 threads): warp 0 = TMA producer (one elected lane), warp 1 = TMEM owner + MMA issuer (one lane),
+// warps 2..5 = epilogue (warp w owns TMEM lanes 32*(w%4)..+31). The accumulator is double-buffered in TMEM so the
+// epilogue of one unit overlaps the main loop of the next. A work unit is (output tile, K-slice); CTA b walks
+// units b, b+grid, b+2*grid, ...
+//
+// Covers the reference's gemm_a16w16_gfx950_kernel / gemm_a16w16_hti_gfx950_kernel
+// (kernels/gemm_a16w16_gfx950.py:378-705, :708-1142), async_load_to_lds (:263-322), the bias/cast/store
+// epilogue (:660-703, :325-375), SplitKProtocol (kernels/gemm_a16w16_gfx950_utils.py:100-299) and
+// BlockSwizzle (kernels/gemm_a16w16_gfx950_utils.py:65-97).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
+
+namespace b200 {
+
+constexpr int kTileP = 128;  // rows of U per CTA tile (MMA M)
+constexpr int kTileK = 64;   // K elements per stage = one 128-byte swizzle span of 16-bit data
+constexpr int kUmmaK = 16;   // K elements per tcgen05.mma kind::f16
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kUStageBytes = kTileP * kTileK * 2;  // 16 KB
+
+struct alignas(64) GemmParams {
+  CUtensorMap tmap_u;
+  CUtensorMap tmap_v;
+  void* out;
+  const void* bias;
+  float* partials;  // [tile][slice][chunk][128][CW] fp32
+  int* tickets;     // [tile]
+  int* status;      // int32[4] or null
+  long long ldo;    // output row stride (elements)
+  int P, Q, K;
+  int tiles_p, tiles_q, num_tiles;
+  int kb_total;  // ceil(K / 64)
+  int split_k;
+  int num_units;
+  int group_p;      // grouped rasterisation over tile rows of P (0 = off)
+  int swap_out;     // 1: D^T is written (out[q*ldo + p]); bias indexed by p
+  int out_dtype;    // 1 fp32, 2 bf16, 3 fp16
+  int in_dtype;     // 2 bf16, 3 fp16
+  int u_mn_major;   // 1: U is P-contiguous, loaded as two [64 P x 64 K] boxes
+  int v_mn_major;   // 1: V is Q-contiguous, loaded as TILE_Q/64 boxes
+  uint32_t idesc;   // tcgen05 instruction descriptor
+  uint32_t u_desc_hi, u_desc_lo;  // smem matrix descriptor without the start address
+  uint32_t v_desc_hi, v_desc_lo;
+  uint32_t u_kstep, v_kstep;  // start-address increment (16-byte units) per K=16 MMA inside a stage
+};
+
+struct Unit {
+  int tile, slice, tp, tq, kb0, kbn;
+};
+
+__device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u) {
+  Unit w;
+  w.tile = u / p.split_k;
+  w.slice = u - w.tile * p.split_k;
+  if (p.group_p > 0) {
+    const int per_group = p.group_p * p.tiles_q;
+    const int g = w.tile / per_group;
+    const int first = g * p.group_p;
+    const int rows = min(p.tiles_p - first, p.group_p);
+    const int r = w.tile - g * per_group;
+    w.tp = first + r % rows;
+    w.tq = r / rows;
+  } else {
+    w.tp = w.tile / p.tiles_q;
+    w.tq = w.tile - w.tp * p.tiles_q;
+  }
+  const int base = p.kb_total / p.split_k, rem = p.kb_total - base * p.split_k;
+  w.kb0 = w.slice * base + min(w.slice, rem);
+  w.kbn = base + (w.slice < rem ? 1 : 0);
+  return w;
+}
+
+template <int TILE_Q, int STAGES>
+struct SmemLayout {
+  static constexpr int kVStageBytes = TILE_Q * kTileK * 2;
+  static constexpr int kStageBytes = kUStageBytes + kVStageBytes;
+  static constexpr int kRingBytes = STAGES * kStageBytes;
+  static constexpr int kBiasOff = kRingBytes;            // float[256]
+  static constexpr int kBarOff = kBiasOff + 256 * 4;     // full[S], empty[S], acc_full[2], acc_empty[2]
+  static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;  // tmem ptr, abort flag, last flag
+  static constexpr int kTotal = kMiscOff + 16;
+  static constexpr int kDynBytes = kTotal + 1024;  // slack for manual 1024-byte alignment
+};
+
+__device__ __forceinline__ void report_abort(const GemmParams& p, int role, int unit) {
+  if (p.status != nullptr) {
+    if (atomicCAS(p.status, 0, 1) == 0) {
+      p.status[1] = blockIdx.x;
+      p.status[2] = role;
+      p.status[3] = unit;
+    }
+  }
+}
+
+// Add bias, cast and store one chunk of CW consecutive Q-columns of one P-row.
+template <int CW>
+__device__ __forceinline__ void finalize_chunk(const GemmParams& p, float (&v)[CW], int prow, int q0,
+                                               const float* bias_q /* smem, chunk-local */, float bias_p) {
+  if (prow >= p.P) return;
+  if (!p.swap_out) {
+    if (p.bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < CW; ++i) v[i] += bias_q[i];
+    }
+    const long long base = (long long)prow * p.ldo + q0;
+    if (p.out_dtype == 1) {
+      float* o = reinterpret_cast<float*>(p.out) + base;
+      if (q0 + CW <= p.Q && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < CW; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < CW; ++i)
+          if (q0 + i < p.Q) o[i] = v[i];
+      }
+    } else {
+      uint32_t pk[CW / 2];
+      if (p.out_dtype == 2) {
+#pragma unroll
+        for (int i = 0; i < CW; i += 2) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(v[i], v[i + 1]);
+          pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < CW; i += 2) {
+          __half2 h = __floats2half2_rn(v[i], v[i + 1]);
+          pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+        }
+      }
+      uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + base;
+      if (q0 + CW <= p.Q && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < CW / 2; i += 4)
+          *reinterpret_cast<uint4*>(o + 2 * i) = make_uint4(pk[i], pk[i + 1], pk[i + 2], pk[i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < CW; ++i)
+          if (q0 + i < p.Q) o[i] = static_cast<uint16_t>((i & 1) ? (pk[i / 2] >> 16) : (pk[i / 2] & 0xffffu));
+      }
+    }
+  } else {
+    // D^T: consecutive lanes hold consecutive p -> each scalar store is warp-coalesced along p.
+#pragma unroll
+    for (int i = 0; i < CW; ++i) {
+      const int q = q0 + i;
+      if (q < p.Q) {
+        const float x = v[i] + bias_p;
+        const long long idx = (long long)q * p.ldo + prow;
+        if (p.out_dtype == 1) {
+          reinterpret_cast<float*>(p.out)[idx] = x;
+        } else if (p.out_dtype == 2) {
+          reinterpret_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(x);
+        } else {
+          reinterpret_cast<__half*>(p.out)[idx] = __float2half_rn(x);
+        }
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float load_in_as_float(const void* ptr, long long i, int in_dtype) {
+  if (in_dtype == 2) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ptr)[i]);
+  return __half2float(reinterpret_cast<const __half*>(ptr)[i]);
+}
+
+template <int TILE_Q, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __grid_constant__ GemmParams p) {
+  using L = SmemLayout<TILE_Q, STAGES>;
+  constexpr int CW = TILE_Q >= 32 ? 32 : 16;  // columns per tcgen05.ld
+  constexpr int NCHUNK = TILE_Q / CW;
+  constexpr uint32_t kTmemCols = (2 * TILE_Q) < 32 ? 32 : 2 * TILE_Q;  // power of two for every TILE_Q in the menu
+  constexpr uint32_t kTxBytes = L::kStageBytes;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw);
+
+  float* bias_s = reinterpret_cast<float*>(sm + L::kBiasOff);
+  const uint32_t bar0 = base + L::kBarOff;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto accf_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto acce_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+  volatile uint32_t* tmem_ptr_s = reinterpret_cast<volatile uint32_t*>(sm + L::kMiscOff);
+  volatile int* abort_s = reinterpret_cast<volatile int*>(sm + L::kMiscOff + 4);
+  volatile int* last_s = reinterpret_cast<volatile int*>(sm + L::kMiscOff + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(accf_bar(b), 1);
+      mbar_init(acce_bar(b), kEpiThreads);
+    }
+    *abort_s = 0;
+    *last_s = 0;
+    fence_mbar_init();
+    prefetch_tmap(&p.tmap_u);
+    prefetch_tmap(&p.tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_ptr_s)), kTmemCols);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_s;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; ok && u < p.num_units; u += gridDim.x) {
+        const Unit w = decode_unit(p, u);
+        const int p0 = w.tp * kTileP, q0 = w.tq * TILE_Q;
+        for (int kb = w.kb0; kb < w.kb0 + w.kbn; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_s)) {
+            report_abort(p, 0, u);
+            ok = false;
+            break;
+          }
+          const uint32_t fb = full_bar(stage);
+          mbar_arrive_expect_tx(fb, kTxBytes);
+          const uint32_t su = base + stage * L::kStageBytes;
+          const uint32_t sv = su + kUStageBytes;
+          const int k0 = kb * kTileK;
+          if (!p.u_mn_major) {
+            tma_load_2d(su, &p.tmap_u, k0, p0, fb);
+          } else {
+            tma_load_2d(su, &p.tmap_u, p0, k0, fb);
+            tma_load_2d(su + 8192u, &p.tmap_u, p0 + 64, k0, fb);
+          }
+          if (!p.v_mn_major) {
+            tma_load_2d(sv, &p.tmap_v, k0, q0, fb);
+          } else {
+#pragma unroll
+            for (int j = 0; j < (TILE_Q >= 64 ? TILE_Q / 64 : 1); ++j) tma_load_2d(sv + 8192u * j, &p.tmap_v, q0 + 64 * j, k0, fb);
+          }
+          ++issued;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Loads already issued still write this CTA's smem: give each one a bounded chance to land.
+        const int pending = issued < STAGES ? issued : STAGES;
+        for (int i = 0; i < pending; ++i) {
+          int s = stage - 1 - i;
+          uint32_t ph = phase;
+          if (s < 0) {
+            s += STAGES;
+            ph ^= 1u;
+          }
+          const unsigned long long t0 = globaltimer_ns();
+          while (!mbar_try_wait(full_bar(s), ph) && globaltimer_ns() - t0 < 100000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; ok && u < p.num_units; u += gridDim.x, ++it) {
+        const Unit w = decode_unit(p, u);
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(acce_bar(buf), acc_phase ^ 1u, abort_s)) {
+          report_abort(p, 1, u);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * TILE_Q;
+        for (int kb = 0; kb < w.kbn; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_s)) {
+            report_abort(p, 2, u);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t su = base + stage * L::kStageBytes;
+          const uint32_t sv = su + kUStageBytes;
+          const uint64_t du = (uint64_t(p.u_desc_hi) << 32) | uint64_t(p.u_desc_lo | ((su >> 4) & 0x3fffu));
+          const uint64_t dv = (uint64_t(p.v_desc_hi) << 32) | uint64_t(p.v_desc_lo | ((sv >> 4) & 0x3fffu));
+#pragma unroll
+          for (int j = 0; j < kTileK / kUmmaK; ++j) {
+            umma_f16<1>(d_tmem, du + uint64_t(j * p.u_kstep), dv + uint64_t(j * p.v_kstep), p.idesc,
+                        (kb | j) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(accf_bar(buf));  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int row = quarter * 32 + lane;
+    const int et = threadIdx.x - 64;  // 0..127
+    int it = 0;
+    for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++it) {
+      const Unit w = decode_unit(p, u);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int prow = w.tp * kTileP + row;
+      const int qbase = w.tq * TILE_Q;
+      const bool direct = (p.split_k == 1);
+
+      // Stage the bias slice of this tile (columns of D) while the main loop runs.
+      float bias_p = 0.f;
+      if (p.bias != nullptr) {
+        if (!p.swap_out) {
+          named_bar_sync(1, kEpiThreads);  // previous unit finished reading bias_s
+          for (int i = et; i < TILE_Q; i += kEpiThreads) {
+            const int q = qbase + i;
+            bias_s[i] = q < p.Q ? load_in_as_float(p.bias, q, p.in_dtype) : 0.f;
+          }
+          named_bar_sync(1, kEpiThreads);
+        } else if (prow < p.P) {
+          bias_p = load_in_as_float(p.bias, prow, p.in_dtype);
+        }
+      }
+
+      if (!mbar_wait<false, false>(accf_bar(buf), acc_phase, abort_s)) {
+        report_abort(p, 3, u);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + buf * TILE_Q + (uint32_t(quarter * 32) << 16);
+      float* part = nullptr;
+      if (!direct) part = p.partials + ((size_t)(w.tile * p.split_k + w.slice) * NCHUNK) * (kTileP * CW) + (size_t)row * CW;
+
+#pragma unroll 1
+      for (int c = 0; c < NCHUNK; ++c) {
+        uint32_t r[32];
+        if constexpr (CW == 32)
+          tmem_ld_32x32(t_acc + c * CW, r);
+        else
+          tmem_ld_32x16(t_acc + c * CW, r);
+        tmem_ld_wait();
+        if (c == NCHUNK - 1) {
+          // Everything this thread needs is in registers: hand the accumulator back to the MMA warp.
+          tc_fence_before();
+          mbar_arrive(acce_bar(buf));
+        }
+        float v[CW];
+#pragma unroll
+        for (int i = 0; i < CW; ++i) v[i] = __uint_as_float(r[i]);
+        if (direct) {
+          finalize_chunk<CW>(p, v, prow, qbase + c * CW, bias_s + c * CW, bias_p);
+        } else {
+          float4* dst = reinterpret_cast<float4*>(part + (size_t)c * (kTileP * CW));
+#pragma unroll
+          for (int i = 0; i < CW; i += 4) __stcg(dst + i / 4, make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]));
+        }
+      }
+
+      if (!direct) {
+        // Ticket: the CTA that arrives last at this tile sums all slices in slice order.
+        __threadfence();
+        named_bar_sync(2, kEpiThreads);
+        if (et == 0) {
+          const int t = atomicAdd(p.tickets + w.tile, 1);
+          const int last = (t == p.split_k - 1) ? 1 : 0;
+          if (last) p.tickets[w.tile] = 0;  // self-cleaning: nobody else touches it until the next launch
+          *last_s = last;
+        }
+        named_bar_sync(2, kEpiThreads);
+        const int last = *last_s;
+        if (last) {
+          __threadfence();
+          const float* tp0 = p.partials + ((size_t)w.tile * p.split_k * NCHUNK) * (kTileP * CW) + (size_t)row * CW;
+#pragma unroll 1
+          for (int c = 0; c < NCHUNK; ++c) {
+            float v[CW];
+#pragma unroll
+            for (int i = 0; i < CW; ++i) v[i] = 0.f;
+            for (int s = 0; s < p.split_k; ++s) {
+              const float4* src = reinterpret_cast<const float4*>(tp0 + ((size_t)s * NCHUNK + c) * (kTileP * CW));
+#pragma unroll
+              for (int i = 0; i < CW; i += 4) {
+                const float4 x = __ldcg(src + i / 4);
+                v[i] += x.x;
+                v[i + 1] += x.y;
+                v[i + 2] += x.z;
+                v[i + 3] += x.w;
+              }
+            }
+            finalize_chunk<CW>(p, v, prow, qbase + c * CW, bias_s + c * CW, bias_p);
+          }
+        }
+        named_bar_sync(2, kEpiThreads);  // last_s may be rewritten by the next unit
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Aligned repack: copies a 16-bit matrix whose base or pitch is not 16-byte aligned (TMA cannot describe it)
+// into a scratch image with a pitch that is a multiple of 8 elements. rows x cols, cols contiguous.
+// The reference rejects such operands (kernels/gemm_a16w16_gfx950.py:1322-1372); this path accepts them.
+__global__ void repack_rows_kernel(const uint16_t* __restrict__ src, long long src_ld, uint16_t* __restrict__ dst,
+                                   long long dst_ld, int rows, int cols) {
+  const int chunks = (cols + 7) >> 3;
+  const long long total = (long long)rows * chunks;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / chunks);
+    const int c0 = (int)(i - (long long)r * chunks) << 3;
+    const uint16_t* s = src + (long long)r * src_ld + c0;
+    uint32_t w[4] = {0, 0, 0, 0};
+    const int n = min(8, cols - c0);
+    if (n == 8 && (reinterpret_cast<uintptr_t>(s) & 7) == 0) {
+      const uint2 a = __ldg(reinterpret_cast<const uint2*>(s));
+      const uint2 b = __ldg(reinterpret_cast<const uint2*>(s) + 1);
+      w[0] = a.x, w[1] = a.y, w[2] = b.x, w[3] = b.y;
+    } else if (n == 8 && (reinterpret_cast<uintptr_t>(s) & 3) == 0) {
+      const uint32_t* s4 = reinterpret_cast<const uint32_t*>(s);
+      w[0] = __ldg(s4), w[1] = __ldg(s4 + 1), w[2] = __ldg(s4 + 2), w[3] = __ldg(s4 + 3);
+    } else {
+      for (int j = 0; j < n; ++j) w[j >> 1] |= uint32_t(__ldg(s + j)) << ((j & 1) * 16);
+    }
+    *reinterpret_cast<uint4*>(dst + (long long)r * dst_ld + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+}  // namespace b200

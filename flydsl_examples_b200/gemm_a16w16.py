@@ -1,0 +1,321 @@
+"""Host side of the B200 A16W16 GEMM: the reference's public call, kept as a drop-in.
+
+    gemm_a16w16(a, b, out=None, bias=None, user_kwargs={}, stream=None, layout="nt", out_dtype=None)
+
+mirrors kernels/gemm_a16w16_gfx950.py:1288-1441 of xytpai/flydsl-examples: same argument meaning, same
+exception types and message prefixes. Underneath it makes one ctypes call into libb200_gemm.so
+(hand-written sm_100a CUDA); there is no Triton, no torch.matmul and no CPU path here.
+
+Accepted inputs are a superset of the reference's: operands whose base or leading stride is not 16-byte
+aligned, 't' A with M not divisible by 8, and any K (K tails) all run. Pass
+``user_kwargs["strict_reference_envelope"]=True`` to get the reference's rejections instead.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from typing import Optional
+
+import torch
+
+from . import _lib
+from . import policy as _policy
+
+GEMM_A16W16_DTYPE_FP32 = _lib.DTYPE_FP32
+GEMM_A16W16_DTYPE_BF16 = _lib.DTYPE_BF16
+GEMM_A16W16_DTYPE_FP16 = _lib.DTYPE_FP16
+
+# The reference's 16-byte DMA granule (kernels/gemm_a16w16_gfx950_utils.py:14); TMA has the same granule.
+DMA_BYTES = 16
+
+_STATUS_WORDS = 4
+_ws_lock = threading.Lock()
+_workspaces: dict[tuple, "_Workspace"] = {}
+_sm_count: dict[int, int] = {}
+
+
+class _Workspace:
+    """Scratch owned by one (device, stream): split-K tickets + fp32 partial tiles + repack images, and the
+    4-word status block kernels write when a bounded wait gives up. Grows on demand, never shrinks.
+    Takes the place of get_split_k_buffers (kernels/gemm_a16w16_gfx950.py:1277-1281)."""
+
+    __slots__ = ("buf", "status")
+
+    def __init__(self, device: torch.device):
+        self.buf = None
+        self.status = torch.zeros(_STATUS_WORDS, dtype=torch.int32, device=device)
+
+    def ensure(self, nbytes: int, device: torch.device, stream: torch.cuda.Stream) -> None:
+        if self.buf is None or self.buf.numel() < nbytes:
+            with torch.cuda.stream(stream):
+                # Zero-filled: the ticket area must start at zero; kernels leave it zero.
+                self.buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+
+
+def _workspace_for(device: torch.device, stream: torch.cuda.Stream) -> _Workspace:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream.cuda_stream)
+    with _ws_lock:
+        ws = _workspaces.get(key)
+        if ws is None:
+            ws = _Workspace(device)
+            _workspaces[key] = ws
+        return ws
+
+
+def _num_sms(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    n = _sm_count.get(idx)
+    if n is None:
+        n = torch.cuda.get_device_properties(idx).multi_processor_count
+        _sm_count[idx] = n
+    return n
+
+
+def _dtype_id(dt: torch.dtype) -> int:
+    if dt is torch.float32:
+        return GEMM_A16W16_DTYPE_FP32
+    if dt is torch.bfloat16:
+        return GEMM_A16W16_DTYPE_BF16
+    if dt is torch.float16:
+        return GEMM_A16W16_DTYPE_FP16
+    raise AssertionError(f"unsupported dtype {dt}")
+
+
+def _dtype_name(dt: torch.dtype) -> str:
+    return {torch.bfloat16: "bf16", torch.float16: "fp16", torch.float32: "fp32"}[dt]
+
+
+def _check_operand(name: str, t: torch.Tensor, transposed: bool, strict: bool, m_for_a: Optional[int]) -> None:
+    """Stride contract of one operand. Mirrors kernels/gemm_a16w16_gfx950.py:1322-1372: the contiguous
+    dimension must have stride 1; in strict mode also the reference's 16-byte rules."""
+    es = t.element_size()
+    if transposed:
+        bad = t.stride(0) != 1
+        lead = t.stride(1)
+        kind = "column-major"
+        want = "stride(0) == 1"
+    else:
+        bad = t.stride(1) != 1
+        lead = t.stride(0)
+        kind = "row-major"
+        want = "stride(1) == 1"
+    extra = ""
+    if strict:
+        bad = bad or t.data_ptr() % DMA_BYTES != 0 or (lead * es) % DMA_BYTES != 0
+        if name == "A" and transposed and m_for_a is not None:
+            vec = DMA_BYTES // es
+            bad = bad or m_for_a % vec != 0
+            extra = f", and M divisible by {vec}"
+        want += f" and a {DMA_BYTES}-byte-aligned data pointer and leading stride"
+    if bad:
+        raise ValueError(
+            f"{name} does not satisfy the layout requirements for a {kind} input: expected {want}{extra}; "
+            f"got shape={tuple(t.shape)} and stride={t.stride()}"
+        )
+
+
+def _strict_k_checks(k: int, kwargs: dict) -> None:
+    """The reference's K-partition rules (kernels/gemm_a16w16_gfx950.py:1239-1274), only in strict mode."""
+    block_k = int(kwargs.get("block_k", 64))
+    split_k = int(kwargs.get("split_k", 1))
+    stages = int(kwargs.get("stages", 2))
+    hti = bool(kwargs.get("use_half_tile_interleaved", True))
+    k_waves = int(kwargs.get("k_waves", 1))
+    working_k = -(-(-(-k // split_k)) // 8) * 8
+    tile_k = block_k * k_waves
+    for s in range(split_k):
+        begin = s * working_k
+        end = min(k, begin + working_k)
+        span = max(0, end - begin)
+        assert span % tile_k == 0, (
+            f"K-tail is unsupported: K={k}, split_k={split_k}, block_k={block_k} leaves a partial K tile"
+        )
+        tiles = span // tile_k
+        if hti:
+            assert tiles >= 2 and tiles % 2 == 0, (
+                f"HTI requires at least two K tiles (an even count) per split; got {tiles}"
+            )
+        else:
+            assert tiles >= stages - 1, f"K-tail is unsupported: {tiles} K tiles cannot fill {stages} stages"
+
+
+def resolve_policy(m: int, n: int, k: int, dtype: torch.dtype, layout: str, user_kwargs: dict,
+                   num_sms: int = _policy.NUM_SMS_DEFAULT) -> _policy.Policy:
+    """user_kwargs -> Policy. An empty dict first consults the tuned JSONL, then the heuristic."""
+    if not user_kwargs:
+        rec = _policy.tuned_lookup(_dtype_name(dtype), layout, m, n, k)
+        if rec is not None:
+            return _policy.from_user_kwargs(rec, m, n, k, layout, num_sms)
+    return _policy.from_user_kwargs(user_kwargs, m, n, k, layout, num_sms)
+
+
+def make_gemm_a16w16_param_and_validate(m: int, n: int, k: int, kwargs: dict):
+    """Shape-dependent policy check: returns the resolved Policy, or None when it cannot run.
+    Same role and name as kernels/gemm_a16w16_gfx950.py:1213-1236 (used by the tuner to filter configs)."""
+    layout = ("t" if kwargs.get("a_is_transposed", False) else "n") + ("t" if kwargs.get("b_is_transposed", True) else "n")
+    user = {key: val for key, val in kwargs.items()
+            if key in _policy.REFERENCE_KEYS or key in _policy.BLACKWELL_KEYS}
+    try:
+        pol = _policy.from_user_kwargs(user, m, n, k, layout)
+    except (ValueError, TypeError):
+        return None
+    return pol if _policy.validate(pol, m, n, k, layout) is None else None
+
+
+def _fill_args(a, b, out, bias, pol: _policy.Policy, a_t: bool, b_t: bool) -> _lib.Args:
+    m, k = a.shape
+    n = b.shape[1]
+    args = _lib.Args()
+    args.a = a.data_ptr()
+    args.b = b.data_ptr()
+    args.out = out.data_ptr()
+    args.bias = bias.data_ptr() if bias is not None else None
+    args.m, args.n, args.k = m, n, k
+    args.lda = a.stride(1) if a_t else a.stride(0)
+    args.ldb = b.stride(1) if b_t else b.stride(0)
+    # A stride of a size-1 dimension is arbitrary in torch; any value >= the extent describes the same memory.
+    min_lda = m if a_t else k
+    min_ldb = k if b_t else n
+    if args.lda < min_lda:
+        args.lda = min_lda
+    if args.ldb < min_ldb:
+        args.ldb = min_ldb
+    args.ldo = n
+    args.a_trans = 1 if a_t else 0
+    args.b_trans = 1 if b_t else 0
+    args.in_dtype = _dtype_id(a.dtype)
+    args.out_dtype = _dtype_id(out.dtype)
+    p = args.policy
+    p.tile_n = pol.tile_n
+    p.stages = pol.stages
+    p.split_k = pol.split_k
+    p.group_m = pol.group_m
+    p.swap_ab = 1 if pol.swap_ab else 0
+    p.cta_group = pol.cta_group
+    p.split_mode = _policy.SPLIT_MODES[pol.split_mode]
+    p.max_ctas = pol.max_ctas
+    p.stream_k = 1 if pol.stream_k else 0
+    return args
+
+
+def gemm_a16w16(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    out: Optional[torch.Tensor] = None,
+    bias: Optional[torch.Tensor] = None,
+    user_kwargs: dict = {},
+    stream: Optional[torch.cuda.Stream] = None,
+    layout: str = "nt",
+    out_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """Compute C[M, N] = A[M, K] @ B[K, N] (+ bias[N]) with fp32 accumulation and one final cast.
+
+    Logical shapes never change with `layout`; each character only states which dimension of that operand is
+    contiguous ('n' row-major, 't' column-major), exactly as in the reference. `out` may be any contiguous
+    tensor with M*N elements; the returned tensor shares its storage. Asynchronous on `stream`.
+    """
+    if stream is None:
+        stream = torch.cuda.current_stream(a.device if a.is_cuda else None)
+    layout = layout.lower()
+    if layout not in ("nn", "nt", "tn", "tt"):
+        raise ValueError(f"unsupported GEMM layout: {layout!r}; expected 'nn', 'nt', 'tn', or 'tt'")
+    a_t = layout[0] == "t"
+    b_t = layout[1] == "t"
+    device = a.device
+    assert a.device == b.device
+    assert a.is_cuda, "gemm_a16w16 runs on CUDA tensors only (there is no CPU path)"
+    assert a.ndim == 2 and b.ndim == 2
+    m, k = a.shape
+    assert b.shape[0] == k
+    n = b.shape[1]
+    assert a.dtype == b.dtype
+    assert a.dtype in (torch.float16, torch.bfloat16)
+
+    strict = bool(user_kwargs.get("strict_reference_envelope", False))
+    _check_operand("A", a, a_t, strict, m)
+    _check_operand("B", b, b_t, strict, None)
+
+    if out_dtype is None:
+        out_dtype = a.dtype if out is None else out.dtype
+    if out_dtype not in (a.dtype, torch.float32):
+        raise ValueError(f"unsupported output dtype {out_dtype}; expected {a.dtype} or torch.float32")
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=device)
+    else:
+        assert out.dtype == out_dtype
+        assert out.device == device
+        assert out.is_contiguous()
+    out = out.view(-1, n)
+    assert out.shape[0] == m
+
+    if bias is not None:
+        if not bias.is_contiguous():
+            bias = bias.contiguous()
+        assert bias.shape[0] == n
+        assert bias.dtype == a.dtype
+
+    if strict:
+        merged = {"block_k": 64, "stages": 2, "split_k": 1, "k_waves": 1, "use_half_tile_interleaved": True}
+        merged.update(user_kwargs)
+        _strict_k_checks(k, merged)
+
+    if m == 0 or n == 0:
+        return out
+    if k == 0:
+        with torch.cuda.stream(stream):
+            if bias is None:
+                out.zero_()
+            else:
+                out.copy_(bias.to(out.dtype).expand(m, n))
+        return out
+
+    pol = resolve_policy(m, n, k, a.dtype, layout, user_kwargs, _num_sms(device))
+    why = _policy.validate(pol, m, n, k, layout)
+    assert why is None, f"unsupported gemm_a16w16 shape/config: {why}"
+
+    args = _fill_args(a, b, out, bias, pol, a_t, b_t)
+    lib = _lib.load()
+    ws = _workspace_for(device, stream)
+    with torch.cuda.device(device):
+        need = lib.b200_gemm_workspace_bytes(C.byref(args))
+        if need:
+            ws.ensure(need, device, stream)
+            args.workspace = ws.buf.data_ptr()
+            args.workspace_bytes = ws.buf.numel()
+        args.status = ws.status.data_ptr()
+        rc = lib.b200_gemm_a16w16(C.byref(args), C.c_void_p(stream.cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"b200_gemm_a16w16 failed ({rc}): {_lib.strerror(rc)}")
+    return out
+
+
+def plan(a: torch.Tensor, b: torch.Tensor, layout: str = "nt", user_kwargs: dict = {},
+         out_dtype: Optional[torch.dtype] = None, bias: Optional[torch.Tensor] = None) -> dict:
+    """What a call with these arguments would launch (tile, stages, grid, workspace, repack flags)."""
+    layout = layout.lower()
+    a_t, b_t = layout[0] == "t", layout[1] == "t"
+    m, k = a.shape
+    n = b.shape[1]
+    out_dtype = out_dtype or a.dtype
+    pol = resolve_policy(m, n, k, a.dtype, layout, user_kwargs)
+    fake_out = torch.empty(0, dtype=out_dtype)
+    args = _fill_args(a, b, fake_out, bias, pol, a_t, b_t)
+    pl = _lib.Plan()
+    rc = _lib.load().b200_gemm_plan_query(C.byref(args), C.byref(pl))
+    if rc != 0:
+        raise RuntimeError(f"b200_gemm_plan_query failed ({rc}): {_lib.strerror(rc)}")
+    return pl.as_dict()
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any kernel launched through gemm_a16w16 on `device` abandoned a bounded wait."""
+    torch.cuda.synchronize(device)
+    with _ws_lock:
+        items = list(_workspaces.items())
+    for (dev, _stream), ws in items:
+        if device is not None and torch.device(device).index not in (None, dev):
+            continue
+        st = ws.status.tolist()
+        if st[0] != 0:
+            ws.status.zero_()
+            raise RuntimeError(f"b200 gemm kernel gave up a bounded wait: code={st[0]} cta={st[1]} role={st[2]} unit={st[3]}")

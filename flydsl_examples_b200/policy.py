@@ -1,0 +1,210 @@
+"""Blackwell tile policy: defaults, validation and the shape heuristic.
+
+Takes the place of the reference's compile-time policy struct and its validators
+(kernels/gemm_a16w16_gfx950.py:33-61 GemmA16W16Gfx950Param, :64-245 make_gemm_a16w16_gfx950_param,
+:1213-1236 make_gemm_a16w16_param_and_validate, :1239-1274 assert_no_k_tail). The reference keys are still
+accepted so that its call sites run unchanged; the keys that describe gfx950 wave layouts have no meaning on
+sm_100a and are ignored.
+"""
+from __future__ import annotations
+
+import json
+import math
+from dataclasses import dataclass, asdict
+from pathlib import Path
+from typing import Optional
+
+TILE_M = 128  # rows per CTA on the MMA M axis (TMEM lanes)
+TILE_K = 64   # one 128-byte swizzle span of 16-bit data
+TILE_N_MENU = (16, 32, 64, 128, 256)
+MAX_STAGES = {16: 10, 32: 10, 64: 8, 128: 6, 256: 4}
+SMEM_LIMIT = 232448
+TMEM_COLUMNS = 512
+NUM_SMS_DEFAULT = 148
+
+# Keys of the reference's policy dict (kernels/gemm_a16w16_gfx950.py:1390-1401).
+REFERENCE_KEYS = (
+    "block_m", "block_n", "block_k", "stages", "split_k", "m_waves", "n_waves", "k_waves", "group_m",
+    "use_half_tile_interleaved",
+)
+# Keys that only exist here.
+BLACKWELL_KEYS = ("tile_n", "swap_ab", "cta_group", "split_mode", "max_ctas", "stream_k")
+CONTROL_KEYS = ("strict_reference_envelope",)
+SPLIT_MODES = {"ticket": 0, "atomic": 1}
+
+
+@dataclass(frozen=True)
+class Policy:
+    tile_n: int
+    stages: int = 0          # 0 = deepest ring that fits
+    split_k: int = 1
+    group_m: int = 0
+    swap_ab: bool = False
+    cta_group: int = 1
+    split_mode: str = "ticket"
+    max_ctas: int = 0
+    stream_k: bool = False
+
+    def as_dict(self) -> dict:
+        return asdict(self)
+
+
+def smem_bytes(tile_n: int, stages: int) -> int:
+    """Dynamic shared memory of one CTA: the ring, the bias slice, the barriers and alignment slack."""
+    return stages * (TILE_M * TILE_K * 2 + tile_n * TILE_K * 2) + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024
+
+
+def split_k_slices(k: int, split_k: int) -> list[tuple[int, int]]:
+    """K-block ranges [(first_block, n_blocks)] of each slice: uneven slices allowed, none empty."""
+    kb = (k + TILE_K - 1) // TILE_K
+    split_k = max(1, min(split_k, kb))
+    base, rem = divmod(kb, split_k)
+    out = []
+    for s in range(split_k):
+        out.append((s * base + min(s, rem), base + (1 if s < rem else 0)))
+    return out
+
+
+def raster(tile: int, tiles_p: int, tiles_q: int, group: int) -> tuple[int, int]:
+    """Tile id -> (tile row, tile column). Groups of `group` tile rows are walked row-fastest, like the
+    GROUP_M part of the reference's BlockSwizzle (kernels/gemm_a16w16_gfx950_utils.py:84-92)."""
+    if group > 0:
+        per_group = group * tiles_q
+        g = tile // per_group
+        first = g * group
+        rows = min(tiles_p - first, group)
+        r = tile - g * per_group
+        return first + r % rows, r // rows
+    return tile // tiles_q, tile % tiles_q
+
+
+def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
+    """Return None when the policy is runnable for this problem, else the reason."""
+    if pol.tile_n not in TILE_N_MENU:
+        return f"tile_n must be one of {TILE_N_MENU}, got {pol.tile_n}"
+    if pol.cta_group not in (1,):
+        return f"cta_group must be 1, got {pol.cta_group}"
+    if pol.stages < 0 or pol.stages == 1 or pol.stages > MAX_STAGES[pol.tile_n]:
+        return f"stages must be 0 (auto) or 2..{MAX_STAGES[pol.tile_n]} for tile_n={pol.tile_n}, got {pol.stages}"
+    if pol.stages and smem_bytes(pol.tile_n, pol.stages) > SMEM_LIMIT:
+        return "shared memory ring exceeds 227 KB"
+    if pol.split_k < 1:
+        return f"split_k must be >= 1, got {pol.split_k}"
+    if pol.split_mode not in SPLIT_MODES:
+        return f"split_mode must be one of {tuple(SPLIT_MODES)}, got {pol.split_mode!r}"
+    if pol.group_m < 0:
+        return f"group_m must be >= 0, got {pol.group_m}"
+    # The operand on the MMA N axis, when it is contiguous along N (or M after a swap), is fetched as 64-wide boxes.
+    a_mn = layout[0] == "t"
+    b_mn = layout[1] == "n"
+    v_mn = a_mn if pol.swap_ab else b_mn
+    if v_mn and pol.tile_n < 64:
+        return "tile_n < 64 needs the tile_n-side operand to be K-contiguous"
+    if 2 * pol.tile_n > TMEM_COLUMNS:
+        return "two accumulators do not fit in 512 TMEM columns"
+    return None
+
+
+def heuristic(m: int, n: int, k: int, layout: str = "nt", num_sms: int = NUM_SMS_DEFAULT) -> Policy:
+    """Shape-driven default used when the caller passes no Blackwell keys."""
+    a_mn = layout[0] == "t"
+    b_mn = layout[1] == "n"
+    kb = max(1, (k + TILE_K - 1) // TILE_K)
+    swap = m <= 64 and n > m
+    if swap:
+        q, v_mn = m, a_mn
+        p_ext = n
+    else:
+        q, v_mn = n, b_mn
+        p_ext = m
+    menu = [t for t in TILE_N_MENU if not (v_mn and t < 64)]
+    tiles_p = (p_ext + TILE_M - 1) // TILE_M
+    if swap:
+        tile_n = next((t for t in menu if t >= q), menu[-1])
+    else:
+        # Larger N tiles reuse each U stage more; smaller ones quantise better on few tiles.
+        eff = {256: 1.0, 128: 0.9, 64: 0.65, 32: 0.4, 16: 0.25}
+        best, best_score = menu[-1], -1.0
+        for t in menu:
+            if t > max(64, 1 << (max(q, 1) - 1).bit_length()):
+                continue
+            tiles = tiles_p * ((q + t - 1) // t)
+            waves = math.ceil(tiles / num_sms)
+            used = (q / (((q + t - 1) // t) * t))
+            score = eff[t] * used * tiles / (waves * num_sms)
+            if score > best_score + 1e-9:
+                best, best_score = t, score
+        tile_n = best
+    tiles = tiles_p * ((q + tile_n - 1) // tile_n)
+    split = 1
+    if tiles * 2 <= num_sms and kb >= 8:
+        split = max(1, min(num_sms // tiles, kb // 4, 64))
+    group = 8 if (tiles >= 2 * num_sms and not swap) else 0
+    return Policy(tile_n=tile_n, split_k=split, group_m=group, swap_ab=swap)
+
+
+def from_user_kwargs(user_kwargs: dict, m: int, n: int, k: int, layout: str, num_sms: int = NUM_SMS_DEFAULT) -> Policy:
+    """Merge a caller's dict over the heuristic. Unknown keys raise ValueError."""
+    known = set(REFERENCE_KEYS) | set(BLACKWELL_KEYS) | set(CONTROL_KEYS)
+    unknown = [key for key in user_kwargs if key not in known]
+    if unknown:
+        raise ValueError(f"unknown gemm_a16w16 policy keys: {sorted(unknown)}")
+    base = heuristic(m, n, k, layout, num_sms)
+    native = any(key in user_kwargs for key in BLACKWELL_KEYS)
+    fields = base.as_dict()
+    if native:
+        # A Blackwell policy is taken literally: nothing the caller left out is second-guessed by the heuristic
+        # except the tile, which falls back to the heuristic's choice.
+        fields.update(split_k=1, group_m=0, swap_ab=False, stages=0)
+        for key in BLACKWELL_KEYS + ("stages", "split_k", "group_m"):
+            if key in user_kwargs:
+                fields[key] = user_kwargs[key]
+        if "tile_n" not in user_kwargs and "swap_ab" in user_kwargs and bool(user_kwargs["swap_ab"]) != base.swap_ab:
+            q = m if fields["swap_ab"] else n
+            v_mn = (layout[0] == "t") if fields["swap_ab"] else (layout[1] == "n")
+            menu = [t for t in TILE_N_MENU if not (v_mn and t < 64)]
+            fields["tile_n"] = next((t for t in menu if t >= q), menu[-1])
+    else:
+        # Reference policy: its split_k / group_m requests carry over, wave and block shapes do not apply.
+        if "split_k" in user_kwargs:
+            fields["split_k"] = int(user_kwargs["split_k"])
+        if "group_m" in user_kwargs:
+            fields["group_m"] = int(user_kwargs["group_m"])
+    fields["swap_ab"] = bool(fields["swap_ab"])
+    fields["stream_k"] = bool(fields["stream_k"])
+    pol = Policy(**fields)
+    return pol
+
+
+# ------------------------------------------------------------------ tuned table (JSONL written by gemm_tune.py)
+_TUNED: dict[tuple, dict] = {}
+_TUNED_LOADED = False
+TUNED_PATH = Path(__file__).resolve().parent.parent / "gemm_a16w16_tuned.jsonl"
+
+
+def load_tuned(path: Optional[Path] = None) -> dict[tuple, dict]:
+    """Read the tuner's JSONL ({arch,dtype,layout,m,n,k,config,duration,tflops} per line; same schema as the
+    reference's gemm_a16w16_tuned.jsonl) keeping only sm_100a rows."""
+    global _TUNED_LOADED
+    path = Path(path) if path else TUNED_PATH
+    table: dict[tuple, dict] = {}
+    if path.exists():
+        for line in path.read_text().splitlines():
+            line = line.strip()
+            if not line:
+                continue
+            rec = json.loads(line)
+            if rec.get("arch") != "sm_100a":
+                continue
+            table[(rec["dtype"], rec["layout"], rec["m"], rec["n"], rec["k"])] = rec["config"]
+    if path == TUNED_PATH:
+        _TUNED.clear()
+        _TUNED.update(table)
+        _TUNED_LOADED = True
+    return table
+
+
+def tuned_lookup(dtype: str, layout: str, m: int, n: int, k: int) -> Optional[dict]:
+    if not _TUNED_LOADED:
+        load_tuned()
+    return _TUNED.get((dtype, layout, m, n, k))

@@ -1,0 +1,117 @@
+/* C ABI of the B200 (sm_100a) A16W16 GEMM library, libb200_gemm.so.
+ *
+ * This is the drop-in boundary for the one hot path of xytpai/flydsl-examples:
+ *   C[M,N] = A[M,K] * B[K,N] (+ bias[N]), 16-bit inputs, fp32 accumulation, one cast to the output type.
+ * Plain pointers and sizes only; no torch types. Every entry point is re-entrant, never synchronises the
+ * device, never throws and never aborts: errors come back as negative codes (b200_gemm_strerror).
+ * Entry points allocate no device memory unless their comment says so.
+ */
+#ifndef B200_GEMM_H_
+#define B200_GEMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype ids: the reference's GEMM_A16W16_DTYPE_{FP32,BF16,FP16} (kernels/gemm_a16w16_gfx950.py:28-30). */
+#define B200_GEMM_DTYPE_FP32 1
+#define B200_GEMM_DTYPE_BF16 2
+#define B200_GEMM_DTYPE_FP16 3
+
+/* error codes */
+#define B200_GEMM_OK 0
+#define B200_GEMM_ERR_BAD_ARG (-1)        /* null pointer, bad dtype, negative size ...            */
+#define B200_GEMM_ERR_BAD_POLICY (-2)     /* tile / stages / split_k outside the supported menu     */
+#define B200_GEMM_ERR_WORKSPACE (-3)      /* workspace missing or smaller than workspace_bytes()    */
+#define B200_GEMM_ERR_TENSOR_MAP (-4)     /* cuTensorMapEncodeTiled refused the operand             */
+#define B200_GEMM_ERR_LAUNCH (-5)         /* CUDA launch error (cudaGetLastError text via strerror) */
+#define B200_GEMM_ERR_DRIVER (-6)         /* driver entry point not found                           */
+#define B200_GEMM_ERR_TOO_LARGE (-7)      /* size beyond a stated fixed limit                       */
+
+/* split-K reduction modes */
+#define B200_GEMM_SPLIT_TICKET 0 /* fp32 partial tiles in the workspace; the last-arriving CTA of a tile sums them in
+                                    slice order, adds bias and casts once (deterministic; never waits)            */
+#define B200_GEMM_SPLIT_ATOMIC 1 /* red.global.add.f32 onto an fp32 output that slice 0 initialised ... not used
+                                    unless asked for; needs fp32 output                                          */
+
+/* Blackwell policy. Replaces the reference's compile-time GemmA16W16Gfx950Param
+ * (kernels/gemm_a16w16_gfx950.py:33-61): block_m/n/k, stages, split_k, *_waves, group_m, HTI flag. */
+typedef struct b200_gemm_policy {
+  int32_t tile_n;     /* MMA N extent of one CTA tile: 16, 32, 64, 128 or 256 (tile M is 128 per CTA; K step 64) */
+  int32_t stages;     /* depth of the TMA->smem ring; 0 = as many as fit in 227 KB                                */
+  int32_t split_k;    /* >= 1 K-slices per output tile (uneven slices allowed, K tail is zero-filled by TMA)      */
+  int32_t group_m;    /* grouped rasterisation: tiles are walked in groups of group_m tile rows; 0 = row-major     */
+  int32_t swap_ab;    /* 1: compute C^T = B^T A^T so N sits on the 128-row MMA axis (small-M shapes)               */
+  int32_t cta_group;  /* 1, or 2 = a CTA pair shares one 256-row tile (tcgen05 cta_group::2)                       */
+  int32_t split_mode; /* B200_GEMM_SPLIT_*                                                                       */
+  int32_t max_ctas;   /* persistent grid size cap; 0 = number of SMs                                              */
+  int32_t stream_k;   /* 1: tail-wave tiles are cut into K spans so every SM gets equal work                      */
+  int32_t reserved[7];
+} b200_gemm_policy;
+
+/* One GEMM call. Replaces the argument list of the reference's jit host stub gemm_a16w16_gfx950
+ * (kernels/gemm_a16w16_gfx950.py:1145-1210): out, a, b, bias, semaphore, signal, split_k, param, stream. */
+typedef struct b200_gemm_args {
+  const void* a;    /* device pointer to A[0,0] (storage offset already applied)                      */
+  const void* b;    /* device pointer to B[0,0]; B is logically [K,N]                                 */
+  void* out;        /* device pointer to C[0,0]; row-major, row stride ldo elements                   */
+  const void* bias; /* device pointer to bias[N] in the input dtype, contiguous; NULL = no bias       */
+  int64_t m, n, k;
+  int64_t lda;       /* A leading stride in elements: row stride when a_trans == 0, column stride when 1 */
+  int64_t ldb;       /* B leading stride in elements: row stride when b_trans == 0, column stride when 1 */
+  int64_t ldo;       /* C row stride in elements                                                          */
+  int32_t a_trans;   /* 0: 'n' A, K contiguous; 1: 't' A, M contiguous                                    */
+  int32_t b_trans;   /* 0: 'n' B, N contiguous; 1: 't' B, K contiguous (stored as [N,K])                  */
+  int32_t in_dtype;  /* B200_GEMM_DTYPE_BF16 or _FP16                                                      */
+  int32_t out_dtype; /* in_dtype or B200_GEMM_DTYPE_FP32                                                   */
+  b200_gemm_policy policy;
+  void* workspace; /* device scratch of at least b200_gemm_workspace_bytes(); its first counter_bytes must be zero
+                      before the first call and are left zero by every call (self-cleaning tickets)             */
+  uint64_t workspace_bytes;
+  int32_t* status; /* device int32[4], or NULL. Written only when a bounded wait inside a kernel gave up:
+                      [0]=error code (1), [1]=CTA, [2]=role, [3]=unit                                         */
+} b200_gemm_args;
+
+/* What a call would do, for tests, the tuner and workspace sizing. */
+typedef struct b200_gemm_plan {
+  int32_t tile_m, tile_n, tile_k, stages, split_k, cta_group, swap_ab, group_m;
+  int32_t tiles_p, tiles_q; /* tile grid over (128-row operand, tile_n operand)                              */
+  int32_t num_units, grid;  /* work units (tile x K-slice) and persistent CTAs                               */
+  int32_t smem_bytes, tmem_cols;
+  int32_t a_repacked, b_repacked; /* 1 when the operand is not TMA-encodable (base or pitch not 16-byte aligned)
+                                     and is first copied into an aligned scratch image in the workspace        */
+  uint64_t counter_bytes, partial_bytes, repack_bytes, workspace_bytes;
+} b200_gemm_plan;
+
+/* Launch the GEMM on `cuda_stream` (a cudaStream_t; NULL = legacy default stream) of the current device.
+ * Replaces: gemm_a16w16 -> run_cached -> gemm_a16w16_gfx950 launch
+ * (kernels/gemm_a16w16_gfx950.py:1434-1440, kernels/common.py:7-39). */
+int b200_gemm_a16w16(const b200_gemm_args* args, void* cuda_stream);
+
+/* Resolve the policy for these arguments without launching.
+ * Replaces: make_gemm_a16w16_param_and_validate + assert_no_k_tail
+ * (kernels/gemm_a16w16_gfx950.py:1213-1274). */
+int b200_gemm_plan_query(const b200_gemm_args* args, b200_gemm_plan* plan);
+
+/* Scratch bytes the call needs (0 = none). Replaces get_split_k_buffers
+ * (kernels/gemm_a16w16_gfx950.py:1277-1281), whose fixed 2 x int32[256] limited split-K to 256 tiles. */
+uint64_t b200_gemm_workspace_bytes(const b200_gemm_args* args);
+
+/* Kernel variant table (for the tuner): number of compiled (tile_n, cta_group) variants and their description.
+ * Replaces the JIT cache of kernels/common.py:7-39 with an ahead-of-time table. */
+int b200_gemm_num_variants(void);
+int b200_gemm_describe_variant(int index, int32_t* tile_n, int32_t* cta_group, int32_t* max_stages);
+
+/* Text for an error code; for B200_GEMM_ERR_LAUNCH the last CUDA error string seen by this thread. */
+const char* b200_gemm_strerror(int code);
+
+/* Library / build identification, e.g. "b200_gemm 0.1 sm_100a". */
+const char* b200_gemm_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_GEMM_H_ */
