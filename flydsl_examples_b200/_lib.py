@@ -89,6 +89,7 @@ EXPORTS = (
     "b200_gemm_workspace_bytes",
     "b200_gemm_num_variants",
     "b200_gemm_describe_variant",
+    "b200_gemm_cast_bias",
     "b200_gemm_strerror",
     "b200_gemm_version",
 )
@@ -128,6 +129,8 @@ def load() -> C.CDLL:
     lib.b200_gemm_num_variants.restype = C.c_int
     lib.b200_gemm_describe_variant.argtypes = [C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.b200_gemm_describe_variant.restype = C.c_int
+    lib.b200_gemm_cast_bias.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]
+    lib.b200_gemm_cast_bias.restype = C.c_int
     lib.b200_gemm_strerror.argtypes = [C.c_int]
     lib.b200_gemm_strerror.restype = C.c_char_p
     lib.b200_gemm_version.argtypes = []

@@ -364,6 +364,24 @@ int b200_gemm_describe_variant(int index, int32_t* tile_n, int32_t* cta_group, i
   return 0;
 }
 
+int b200_gemm_cast_bias(const float* in, void* out, const void* bias, int64_t rows, int64_t cols, int32_t out_dtype,
+                        int32_t bias_dtype, void* cuda_stream) {
+  if (in == nullptr || out == nullptr || rows < 0 || cols <= 0 || cols > 0x7fffffffLL) return B200_GEMM_ERR_BAD_ARG;
+  if (out_dtype < 1 || out_dtype > 3) return B200_GEMM_ERR_BAD_ARG;
+  if (bias != nullptr && bias_dtype != B200_GEMM_DTYPE_BF16 && bias_dtype != B200_GEMM_DTYPE_FP16) return B200_GEMM_ERR_BAD_ARG;
+  if (cols % 4 != 0 || (reinterpret_cast<uintptr_t>(in) & 15) != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0)
+    return B200_GEMM_ERR_BAD_ARG;
+  if (rows == 0) return 0;
+  const long long total4 = rows * cols / 4;
+  const long long want = (total4 + 255) / 256;
+  const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+  b200::cast_bias_rows_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(in, out, bias, rows, (int)cols,
+                                                                                             out_dtype, bias_dtype);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return b200::set_cuda_error(e);
+  return 0;
+}
+
 const char* b200_gemm_strerror(int code) {
   switch (code) {
     case B200_GEMM_OK: return "ok";

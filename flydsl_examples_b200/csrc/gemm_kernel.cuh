@@ -464,4 +464,32 @@ __global__ void repack_rows_kernel(const uint16_t* __restrict__ src, long long s
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// fp32 [rows, cols] (+ bias[cols] in `bias_dtype`) -> 16-bit or fp32 [rows, cols]; both row-major contiguous.
+// Final step of the K-sharded multi-GPU mode: the fp32 partial sums have been reduced across GPUs and are
+// rounded once here, exactly like the single-GPU epilogue.
+__global__ void cast_bias_rows_kernel(const float* __restrict__ in, void* __restrict__ out, const void* __restrict__ bias,
+                                      long long rows, int cols, int out_dtype, int bias_dtype) {
+  const long long total4 = rows * (long long)cols / 4;  // cols % 4 == 0 is checked by the host
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+    float4 x = __ldcs(reinterpret_cast<const float4*>(in) + i);
+    if (bias != nullptr) {
+      const int c = (int)((i * 4) % cols);
+      x.x += load_in_as_float(bias, c, bias_dtype);
+      x.y += load_in_as_float(bias, c + 1, bias_dtype);
+      x.z += load_in_as_float(bias, c + 2, bias_dtype);
+      x.w += load_in_as_float(bias, c + 3, bias_dtype);
+    }
+    if (out_dtype == 1) {
+      reinterpret_cast<float4*>(out)[i] = x;
+    } else if (out_dtype == 2) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+      reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    } else {
+      __half2 lo = __floats2half2_rn(x.x, x.y), hi = __floats2half2_rn(x.z, x.w);
+      reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+  }
+}
+
 }  // namespace b200

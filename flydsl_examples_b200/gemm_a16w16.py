@@ -115,28 +115,32 @@ def _check_operand(name: str, t: torch.Tensor, transposed: bool, strict: bool, m
 
 
 def _strict_k_checks(k: int, kwargs: dict) -> None:
-    """The reference's K-partition rules (kernels/gemm_a16w16_gfx950.py:1239-1274), only in strict mode."""
-    block_k = int(kwargs.get("block_k", 64))
-    split_k = int(kwargs.get("split_k", 1))
-    stages = int(kwargs.get("stages", 2))
-    hti = bool(kwargs.get("use_half_tile_interleaved", True))
-    k_waves = int(kwargs.get("k_waves", 1))
-    working_k = -(-(-(-k // split_k)) // 8) * 8
-    tile_k = block_k * k_waves
-    for s in range(split_k):
-        begin = s * working_k
-        end = min(k, begin + working_k)
-        span = max(0, end - begin)
-        assert span % tile_k == 0, (
-            f"K-tail is unsupported: K={k}, split_k={split_k}, block_k={block_k} leaves a partial K tile"
-        )
-        tiles = span // tile_k
+    """The reference's K-partition rules (kernels/gemm_a16w16_gfx950.py:1239-1274), applied only in strict
+    mode: every split must be a whole number of block_k tiles, at least stages-1 of them, and an even count of
+    at least two for its half-tile-interleaved kernel. The B200 kernels have none of these limits."""
+    block_k = int(kwargs["block_k"])
+    split_k = int(kwargs["split_k"])
+    stages = int(kwargs["stages"])
+    hti = bool(kwargs["use_half_tile_interleaved"])
+    granule = DMA_BYTES // 2
+    per_split = -(-k // split_k)
+    per_split = -(-per_split // granule) * granule
+    last = k - (split_k - 1) * per_split
+    assert per_split % block_k == 0, (
+        f"K-tail is unsupported: split-K partition of {per_split} elements is not a multiple of block_k={block_k}"
+    )
+    assert last > 0 and last % block_k == 0, (
+        f"K-tail is unsupported: last split-K partition of {last} elements must be a positive multiple of "
+        f"block_k={block_k}"
+    )
+    need = stages - 1
+    for span, which in ((per_split, "each"), (last, "the last")):
+        tiles = span // block_k
+        assert tiles >= need, f"{which} split-K partition needs at least {need} K tiles, got {tiles}"
         if hti:
             assert tiles >= 2 and tiles % 2 == 0, (
-                f"HTI requires at least two K tiles (an even count) per split; got {tiles}"
+                f"HTI requires at least two K tiles, and an even count, in {which} split-K partition; got {tiles}"
             )
-        else:
-            assert tiles >= stages - 1, f"K-tail is unsupported: {tiles} K tiles cannot fill {stages} stages"
 
 
 def resolve_policy(m: int, n: int, k: int, dtype: torch.dtype, layout: str, user_kwargs: dict,
@@ -214,8 +218,6 @@ def gemm_a16w16(
     contiguous ('n' row-major, 't' column-major), exactly as in the reference. `out` may be any contiguous
     tensor with M*N elements; the returned tensor shares its storage. Asynchronous on `stream`.
     """
-    if stream is None:
-        stream = torch.cuda.current_stream(a.device if a.is_cuda else None)
     layout = layout.lower()
     if layout not in ("nn", "nt", "tn", "tt"):
         raise ValueError(f"unsupported GEMM layout: {layout!r}; expected 'nn', 'nt', 'tn', or 'tt'")
@@ -223,7 +225,6 @@ def gemm_a16w16(
     b_t = layout[1] == "t"
     device = a.device
     assert a.device == b.device
-    assert a.is_cuda, "gemm_a16w16 runs on CUDA tensors only (there is no CPU path)"
     assert a.ndim == 2 and b.ndim == 2
     m, k = a.shape
     assert b.shape[0] == k
@@ -259,6 +260,9 @@ def gemm_a16w16(
         merged.update(user_kwargs)
         _strict_k_checks(k, merged)
 
+    assert a.is_cuda, "gemm_a16w16 runs on CUDA tensors only (there is no CPU path)"
+    if stream is None:
+        stream = torch.cuda.current_stream(device)
     if m == 0 or n == 0:
         return out
     if k == 0:

@@ -105,6 +105,13 @@ uint64_t b200_gemm_workspace_bytes(const b200_gemm_args* args);
 int b200_gemm_num_variants(void);
 int b200_gemm_describe_variant(int index, int32_t* tile_n, int32_t* cta_group, int32_t* max_stages);
 
+/* out[rows, cols] = cast(in[rows, cols] (fp32) + bias[cols]); row-major contiguous, cols % 4 == 0, 16-byte aligned
+ * pointers. Last step of the K-sharded multi-GPU mode (fp32 partial sums reduced over NVLink, then rounded once).
+ * Restates, for that mode, the cast + bias of the reference epilogue (kernels/gemm_a16w16_gfx950.py:541-550,
+ * :660-661); the reference itself has no multi-GPU path. */
+int b200_gemm_cast_bias(const float* in, void* out, const void* bias, int64_t rows, int64_t cols, int32_t out_dtype,
+                        int32_t bias_dtype, void* cuda_stream);
+
 /* Text for an error code; for B200_GEMM_ERR_LAUNCH the last CUDA error string seen by this thread. */
 const char* b200_gemm_strerror(int code);
 

@@ -1,0 +1,341 @@
+"""GPU parity of the CUDA path against the CPU oracle, through the public call (one ctypes hop into the C ABI).
+
+Tolerance is the build contract's: rtol 1e-2 / atol 1e-2*sqrt(K/1024) for 16-bit outputs, rtol 2e-3 /
+atol 2e-3*sqrt(K/1024) for fp32 outputs, the same bound with split-K. Case lists follow the reference's tests
+(test_gemm_a16w16_gfx950.py:253-1031) re-parametrised by Blackwell policies, plus the five benchmark configs.
+"""
+import functools
+
+import pytest
+import torch
+
+from flydsl_examples_b200.gemm_a16w16 import check_status, plan
+from kernels.gemm_a16w16_gfx950 import gemm_a16w16
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+DT = {"bf16": torch.bfloat16, "fp16": torch.float16}
+LAYOUTS = ("nn", "nt", "tn", "tt")
+
+
+def run_case(case: O.Case, repeats: int = 1, prefill="nan"):
+    a, b, bias, a_l, b_l, bias_l = O.build_inputs(case, device=DEV)
+    ref = O.reference_matmul(a_l, b_l, bias_l, case.torch_out_dtype)
+    res = None
+    for _ in range(repeats):
+        if prefill == "nan":
+            out = torch.full((case.m, case.n), float("nan"), dtype=case.torch_out_dtype, device=DEV)
+        else:  # the reference pre-fills outputs with randn (test_gemm_a16w16_gfx950.py:76-79)
+            out = torch.randn((case.m, case.n), dtype=case.torch_out_dtype, device=DEV)
+        got = gemm_a16w16(a, b, out, bias=bias, user_kwargs=case.user_kwargs, layout=case.layout)
+        check_status()
+        assert got.data_ptr() == out.data_ptr()
+        res = O.assert_close(got, ref, case.k, f"{case.name} {case.user_kwargs}")
+    return res
+
+
+def sampled_check(got, a_l, b_l, bias_l, k, out_dtype, n_rows=64, n_cols=64, seed=0):
+    """Full rows and full columns of the product against the CPU oracle (for shapes whose full fp32 CPU matmul
+    would take minutes)."""
+    m, n = got.shape
+    g = torch.Generator().manual_seed(seed)
+    rows = torch.unique(torch.cat([torch.tensor([0, m - 1]), torch.randint(0, m, (n_rows,), generator=g)]))
+    cols = torch.unique(torch.cat([torch.tensor([0, n - 1]), torch.randint(0, n, (n_cols,), generator=g)]))
+    ref_rows = O.reference_matmul(a_l[rows], b_l, bias_l, out_dtype)
+    O.assert_close(got[rows.to(got.device)], ref_rows, k, "sampled rows")
+    ref_cols = O.reference_matmul(a_l, b_l[:, cols], None if bias_l is None else bias_l[cols], out_dtype)
+    O.assert_close(got[:, cols.to(got.device)], ref_cols, k, "sampled cols")
+
+
+# ------------------------------------------------------------------------------------------ benchmark configs
+def test_config1_bf16_nt_256x512x1024():
+    run_case(O.CONFIGS["c1"], repeats=3)
+
+
+@pytest.mark.parametrize("kw", [{}, {"tile_n": 256, "group_m": 8}, {"tile_n": 128, "stages": 6}])
+def test_config2_bf16_nt_bias(kw):
+    case = O.CONFIGS["c2"]
+    run_case(O.Case(**{**case.__dict__, "user_kwargs": kw}))
+
+
+@pytest.mark.parametrize("split_k", [1, 8, 14, 16, 28, 32])
+@pytest.mark.parametrize("swap", [True, False])
+def test_config3_small_m_split_k_fp32(split_k, swap):
+    case = O.CONFIGS["c3"]
+    kw = {"tile_n": 32 if swap else 128, "swap_ab": swap, "split_k": split_k}
+    run_case(O.Case(**{**case.__dict__, "user_kwargs": kw}), repeats=2)
+
+
+def test_config3_default_policy():
+    run_case(O.CONFIGS["c3"], repeats=5, prefill="randn")
+
+
+@functools.lru_cache(maxsize=1)
+def _c4_reference():
+    case = O.CONFIGS["c4_nn"]
+    a_l, b_l, bias_l = O.draw_logical(case)
+    return a_l, b_l, bias_l, O.reference_matmul(a_l, b_l, bias_l, torch.float32)
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("kw", [{}, {"tile_n": 128, "split_k": 2}])
+def test_config4_fp16_padded_offset_ktail(layout, kw):
+    case = O.CONFIGS[f"c4_{layout}"]
+    a_l, b_l, bias_l, ref = _c4_reference()
+    a = O.place(a_l, layout[0] == "t", case.pad, case.offset, DEV)
+    b = O.place(b_l, layout[1] == "t", case.pad, case.offset, DEV)
+    # K-contiguous operands have an 8328-byte pitch here: TMA cannot describe them, the repack path must run
+    pl = plan(a, b, layout, kw, out_dtype=torch.float32)
+    assert pl["a_repacked"] == (1 if layout[0] == "n" else 0)
+    assert pl["b_repacked"] == (1 if layout[1] == "t" else 0)
+    out = torch.full((case.m, case.n), float("nan"), dtype=torch.float32, device=DEV)
+    got = gemm_a16w16(a, b, out, bias=bias_l.to(DEV), user_kwargs=kw, layout=layout)
+    check_status()
+    O.assert_close(got, ref, case.k, f"c4 {layout} {kw}")
+
+
+def test_config5_large_bf16_sampled_and_consistent():
+    case = O.CONFIGS["c5"]
+    a_l, b_l, bias_l = O.draw_logical(case)
+    a, b = a_l.to(DEV), b_l.t().contiguous().to(DEV).t()
+    out = torch.full((case.m, case.n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    got = gemm_a16w16(a, b, out, layout="nt")
+    check_status()
+    assert bool(torch.isfinite(got).all())
+    sampled_check(got, a_l, b_l, None, case.k, torch.bfloat16, n_rows=48, n_cols=48)
+    # size-independent property: an N-slab computed on its own equals the same columns of the full product
+    n0, n1 = 7168, 7168 + 3584
+    slab = gemm_a16w16(a, b[:, n0:n1], layout="nt")
+    check_status()
+    assert torch.equal(slab, got[:, n0:n1])
+    # secondary cross-check of the whole matrix against the library GEMM on the same GPU
+    lib = torch.matmul(a, b)
+    O.assert_close(got, lib, case.k, "c5 vs torch.matmul (secondary)")
+
+
+# ------------------------------------------------------------------------------------------ reference case lists
+MAIN_LOOP = [  # (m, n, k, kw)  cf. test_gemm_a16w16_gfx950.py:262-283
+    (1024, 1024, 1024, {"tile_n": 256}),
+    (1024, 1024, 1024, {"tile_n": 128, "group_m": 4}),
+    (1056, 1056, 2048 - 64, {"tile_n": 256, "group_m": 4}),   # boundary tiles, odd K-tile count
+    (1056, 1056, 1024 + 64, {"tile_n": 64, "stages": 3}),
+    (512, 768, 4096, {"tile_n": 128, "stages": 2}),
+    (2048, 2048, 512, {}),
+]
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("idx", range(len(MAIN_LOOP)))
+def test_main_loop_shapes(layout, dtype, idx):
+    m, n, k, kw = MAIN_LOOP[idx]
+    run_case(O.Case("main", dtype, layout, m, n, k, seed=100 + idx, bias_std=(0.5 if idx % 2 else None), user_kwargs=kw))
+
+
+SPLIT_K = [  # cf. test_gemm_a16w16_gfx950.py:327-385
+    (32, 384, 7168, {"tile_n": 64, "split_k": 8}),
+    (3, 5120, 2880, {"tile_n": 64, "split_k": 3}),
+    (65, 96, 1024, {"tile_n": 64, "split_k": 2}),
+    (129, 136, 1536, {"tile_n": 128, "split_k": 3}),
+    (257, 264, 2048, {"tile_n": 64, "split_k": 4}),
+    (257, 264, 2048, {"tile_n": 256, "split_k": 8}),
+    (800, 384, 7168, {"tile_n": 128, "split_k": 4}),
+    (64, 64, 512, {"tile_n": 64, "split_k": 2}),
+    (576, 256, 4096, {"tile_n": 64, "split_k": 7, "group_m": 2}),
+]
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("idx", range(len(SPLIT_K)))
+def test_split_k_shapes(layout, dtype, idx):
+    m, n, k, kw = SPLIT_K[idx]
+    for out_dtype in (None, "fp32"):
+        run_case(O.Case("split", dtype, layout, m, n, k, seed=200 + idx, bias_std=0.5, out_dtype=out_dtype, user_kwargs=kw),
+                 repeats=2, prefill="randn")
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("bias", [False, True])
+@pytest.mark.parametrize("split_k", [1, 3])
+def test_fp32_output_64x64x768(layout, dtype, bias, split_k):
+    run_case(O.Case("fp32out", dtype, layout, 64, 64, 768, seed=7, bias_std=1.0 if bias else None, out_dtype="fp32",
+                    user_kwargs={"tile_n": 64, "split_k": split_k}))
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("m", [1, 3, 8, 17])
+def test_small_m(layout, dtype, m):
+    # M = 3 with a column-major A is rejected by the reference (M % 8); it runs here.
+    for kw in ({}, {"tile_n": 64}, {"tile_n": 64, "swap_ab": True, "split_k": 2}):
+        run_case(O.Case("small_m", dtype, layout, m, 32, 512, seed=m, bias_std=0.5, user_kwargs=kw))
+        run_case(O.Case("small_m_wide", dtype, layout, m, 1000, 200, seed=m, user_kwargs=kw))
+
+
+@pytest.mark.parametrize("tile_n", [16, 32])
+@pytest.mark.parametrize("swap", [False, True])
+def test_narrow_tiles_k_contiguous(tile_n, swap):
+    layout = "nt"
+    m, n = (24, 300) if swap else (300, 24)
+    for dtype in ("bf16", "fp16"):
+        run_case(O.Case("narrow", dtype, layout, m, n, 640, seed=5, bias_std=0.3, user_kwargs={"tile_n": tile_n, "swap_ab": swap}))
+        run_case(O.Case("narrow_split", dtype, layout, m, n, 2000, seed=6, bias_std=0.3, out_dtype="fp32",
+                        user_kwargs={"tile_n": tile_n, "swap_ab": swap, "split_k": 5}))
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+def test_exhaustive_edge_residues(layout):
+    # every residue class of M mod 8 and N mod 8 around one tile, K around one K block
+    for m in (121, 128, 129, 135):
+        for n in (57, 64, 65, 71, 72):
+            for k in (1, 8, 63, 64, 65, 72):
+                run_case(O.Case("edge", "fp16", layout, m, n, k, seed=m * n + k, bias_std=0.2, out_dtype="fp32",
+                                pad=8 if layout == "nt" else 0, user_kwargs={"tile_n": 64}))
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+@pytest.mark.parametrize("split_k", [1, 2])
+def test_padded_stride_and_storage_offset(layout, split_k):
+    # cf. test_gemm_a16w16_gfx950.py:688-766: one leading row skipped, 8 leading columns skipped, pitch padded
+    m = n = 64
+    k = 256
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(9)
+
+    def padded(rows, cols, padding, is_t):
+        lead, other = (rows, cols) if is_t else (cols, rows)
+        storage = torch.full((other + 1, lead + padding), float("nan"), dtype=dtype, device=DEV)
+        logical = (torch.rand(rows, cols, generator=g) * 2 - 1).to(dtype)
+        view = storage[1:, 8:8 + lead]
+        view.copy_((logical.t() if is_t else logical).to(DEV))
+        return (view.t() if is_t else view), logical
+
+    a, a_l = padded(m, k, 32, layout[0] == "t")
+    b, b_l = padded(k, n, 48, layout[1] == "t")
+    assert not a.is_contiguous() and not b.is_contiguous() and a.storage_offset() > 0
+    bias_l = (torch.rand(n, generator=g) * 2 - 1).to(dtype)
+    out = torch.empty((m, n), dtype=dtype, device=DEV)
+    kw = {"block_m": 64, "block_n": 64, "block_k": 64, "stages": 2, "split_k": split_k, "m_waves": 2, "n_waves": 2,
+          "group_m": 0, "use_half_tile_interleaved": True}
+    res = gemm_a16w16(a, b, out, bias=bias_l.to(DEV), user_kwargs=kw, layout=layout)
+    check_status()
+    assert res.data_ptr() == out.data_ptr()
+    O.assert_close(out, O.reference_matmul(a_l, b_l, bias_l, dtype), k, f"padded {layout}")
+
+
+@pytest.mark.parametrize("layout", LAYOUTS)
+def test_unaligned_base_and_odd_pitch(layout):
+    # base pointer 2 bytes off a 16-byte boundary and an odd pitch: the reference rejects this, the repack path runs it
+    run_case(O.Case("unaligned", "bf16", layout, 150, 200, 333, seed=21, bias_std=0.5, pad=3, offset=1, user_kwargs={"tile_n": 64}))
+    run_case(O.Case("unaligned_split", "fp16", layout, 150, 200, 1333, seed=22, out_dtype="fp32", pad=1, offset=7,
+                    user_kwargs={"tile_n": 128, "split_k": 3}))
+
+
+def test_allocates_output_with_default_policy():
+    a_l = torch.randn(64, 256).to(torch.bfloat16)
+    b_l = torch.randn(256, 64).to(torch.bfloat16)
+    a = a_l.to(DEV)
+    b = b_l.t().contiguous().to(DEV).t()
+    out = gemm_a16w16(a, b)
+    check_status()
+    assert out.shape == (64, 64) and out.dtype is torch.bfloat16 and out.device == a.device
+    O.assert_close(out, O.reference_matmul(a_l, b_l, None, torch.bfloat16), 256)
+    out32 = gemm_a16w16(a, b, out_dtype=torch.float32)
+    assert out32.dtype is torch.float32
+    O.assert_close(out32, O.reference_matmul(a_l, b_l, None, torch.float32), 256)
+
+
+def test_out_may_be_nd_and_result_aliases_it():
+    a_l = torch.randn(96, 128).to(torch.float16)
+    b_l = torch.randn(128, 80).to(torch.float16)
+    out = torch.full((4, 24, 80), float("nan"), dtype=torch.float16, device=DEV)
+    got = gemm_a16w16(a_l.to(DEV), b_l.to(DEV), out, layout="nn")
+    check_status()
+    assert got.shape == (96, 80) and got.data_ptr() == out.data_ptr()
+    O.assert_close(out.view(96, 80), O.reference_matmul(a_l, b_l, None, torch.float16), 128)
+
+
+def test_strided_bias_is_made_contiguous():
+    a_l = torch.randn(64, 256).to(torch.bfloat16)
+    b_l = torch.randn(256, 64).to(torch.bfloat16)
+    bias_storage = torch.randn(128).to(torch.bfloat16)
+    bias = bias_storage.to(DEV)[::2]
+    assert not bias.is_contiguous()
+    out = gemm_a16w16(a_l.to(DEV), b_l.t().contiguous().to(DEV).t(), bias=bias, layout="nt")
+    check_status()
+    O.assert_close(out, O.reference_matmul(a_l, b_l, bias_storage[::2], torch.bfloat16), 256)
+
+
+@pytest.mark.parametrize("n", [4096, 4032])
+def test_grouped_raster_boundary_paths(n):
+    # cf. test_gemm_a16w16_gfx950.py:890-909: ragged last group of tile rows
+    run_case(O.Case("raster", "bf16", "nt", 320, n, 256, seed=n, user_kwargs={"tile_n": 64, "group_m": 4}), repeats=2)
+    run_case(O.Case("raster2", "bf16", "nt", 5 * 128 + 7, 777, 192, seed=n, user_kwargs={"tile_n": 64, "group_m": 3}))
+
+
+def test_split_k_workspaces_are_per_stream():
+    # cf. test_gemm_a16w16_gfx950.py:933-998: two streams running split-K at once must not share tickets/partials
+    case = O.Case("streams", "bf16", "nt", 256, 512, 4096, seed=31, bias_std=0.5, user_kwargs={"tile_n": 64, "split_k": 8})
+    a, b, bias, a_l, b_l, bias_l = O.build_inputs(case, device=DEV)
+    ref = O.reference_matmul(a_l, b_l, bias_l, torch.bfloat16)
+    outs = [torch.full((256, 512), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    torch.cuda.synchronize()
+    for rep in range(10):
+        for s, o in zip(streams, outs):
+            with torch.cuda.stream(s):
+                gemm_a16w16(a, b, o, bias=bias, user_kwargs=case.user_kwargs, layout="nt", stream=s)
+    for s in streams:
+        s.synchronize()
+    check_status()
+    for o in outs:
+        O.assert_close(o, ref, case.k, "two streams")
+
+
+def test_repeated_calls_leave_tickets_clean():
+    case = O.Case("repeat", "fp16", "tn", 300, 200, 3000, seed=41, bias_std=0.5, out_dtype="fp32", user_kwargs={"tile_n": 64, "split_k": 6})
+    run_case(case, repeats=5, prefill="randn")
+    # a different split-K shape right after, on the same workspace
+    run_case(O.Case("repeat2", "fp16", "nt", 100, 700, 1000, seed=42, user_kwargs={"tile_n": 128, "split_k": 4}), repeats=2)
+
+
+def test_zero_sized_and_k_zero():
+    a = torch.empty(0, 64, dtype=torch.bfloat16, device=DEV)
+    b = torch.empty(64, 32, dtype=torch.bfloat16, device=DEV)
+    assert gemm_a16w16(a, b, layout="nn").shape == (0, 32)
+    bias = torch.randn(32).to(torch.bfloat16)
+    out = gemm_a16w16(torch.empty(5, 0, dtype=torch.bfloat16, device=DEV), torch.empty(0, 32, dtype=torch.bfloat16, device=DEV),
+                      bias=bias.to(DEV), layout="nn")
+    assert torch.equal(out.cpu(), bias.expand(5, 32))
+
+
+def test_integer_inputs_are_exact_in_every_layout():
+    g = torch.Generator().manual_seed(2)
+    a_l = torch.randint(-3, 4, (200, 328), generator=g).float()
+    b_l = torch.randint(-3, 4, (328, 264), generator=g).float()
+    want = a_l @ b_l
+    for layout in LAYOUTS:
+        for dt in (torch.bfloat16, torch.float16):
+            a = O.place(a_l.to(dt), layout[0] == "t", device=DEV)
+            b = O.place(b_l.to(dt), layout[1] == "t", device=DEV)
+            got = gemm_a16w16(a, b, layout=layout, out_dtype=torch.float32, user_kwargs={"tile_n": 64, "split_k": 2})
+            check_status()
+            assert torch.equal(got.cpu(), want), (layout, dt)
+
+
+def test_linearity_at_full_config2_size():
+    # size-independent property: (A1 + A2) B == A1 B + A2 B when the sums are exact (integers)
+    g = torch.Generator().manual_seed(8)
+    m, n, k = 2048, 4096, 4096
+    a1 = torch.randint(-2, 3, (m, k), generator=g).to(torch.bfloat16).to(DEV)
+    a2 = torch.randint(-2, 3, (m, k), generator=g).to(torch.bfloat16).to(DEV)
+    b = torch.randint(-2, 3, (n, k), generator=g).to(torch.bfloat16).to(DEV).t()
+    f = lambda x: gemm_a16w16(x, b, layout="nt", out_dtype=torch.float32)
+    lhs = f(a1 + a2)
+    rhs = f(a1) + f(a2)
+    check_status()
+    assert torch.equal(lhs, rhs)

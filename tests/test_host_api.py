@@ -1,0 +1,191 @@
+"""Host-side logic on CPU: policy resolution, validation, the error contract of the public call (the reference's
+negative tests, test_gemm_a16w16_gfx950.py:810-858 and :1001-1031), scheduler arithmetic. No GPU, no kernels."""
+import pytest
+import torch
+
+from flydsl_examples_b200 import policy as P
+from flydsl_examples_b200.gemm_a16w16 import gemm_a16w16, make_gemm_a16w16_param_and_validate, plan
+from kernels.gemm_a16w16_gfx950 import GEMM_A16W16_DTYPE_BF16, GEMM_A16W16_DTYPE_FP16, GEMM_A16W16_DTYPE_FP32
+from kernels.gemm_a16w16_gfx950_utils import GFX950_DMA_BYTES
+
+REF_KW = {"block_m": 64, "block_n": 64, "block_k": 64, "stages": 2, "m_waves": 2, "n_waves": 2, "group_m": 0}
+
+
+def _mat(rows, cols, dtype, is_t):
+    return torch.empty(cols, rows, dtype=dtype).t() if is_t else torch.empty(rows, cols, dtype=dtype)
+
+
+def test_reexported_names():
+    assert (GEMM_A16W16_DTYPE_FP32, GEMM_A16W16_DTYPE_BF16, GEMM_A16W16_DTYPE_FP16) == (1, 2, 3)
+    assert GFX950_DMA_BYTES == 16
+
+
+def test_bad_layout_is_value_error():
+    a, b = torch.empty(8, 8, dtype=torch.bfloat16), torch.empty(8, 8, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="unsupported GEMM layout"):
+        gemm_a16w16(a, b, layout="xy")
+
+
+@pytest.mark.parametrize(("operand", "layout"), [("A", "nn"), ("A", "tn"), ("B", "nn"), ("B", "nt")])
+def test_rejects_wrong_contiguous_dim(operand, layout):
+    m = n = 64
+    k = 256
+    dt = torch.bfloat16
+    a = _mat(m, k, dt, layout[0] == "t")
+    b = _mat(k, n, dt, layout[1] == "t")
+    if operand == "A":
+        a = torch.empty(m, k, dtype=dt) if layout[0] == "t" else torch.empty(m, 2 * k, dtype=dt)[:, ::2]
+    else:
+        b = torch.empty(k, n, dtype=dt) if layout[1] == "t" else torch.empty(k, 2 * n, dtype=dt)[:, ::2]
+    with pytest.raises(ValueError, match=rf"^{operand} does not satisfy"):
+        gemm_a16w16(a, b, layout=layout)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_strict_mode_rejects_unaligned_m_for_column_major_a(dtype):
+    vec = GFX950_DMA_BYTES // 2
+    m, n, k = vec + 1, 64, 256
+    a = torch.empty(k, 2 * vec, dtype=dtype)[:, :m].t()
+    b = torch.empty(k, n, dtype=dtype)
+    with pytest.raises(ValueError, match=rf"M divisible by {vec}"):
+        gemm_a16w16(a, b, layout="tn", user_kwargs={"strict_reference_envelope": True})
+
+
+@pytest.mark.parametrize(("k", "hti", "message"), [(480, False, "K-tail is unsupported"), (64, True, "HTI requires at least two"), (192, True, "HTI requires at least two")])
+def test_strict_mode_rejects_k_partitioning(k, hti, message):
+    a = torch.empty(64, k, dtype=torch.bfloat16)
+    b = _mat(k, 64, torch.bfloat16, True)
+    kw = dict(REF_KW, use_half_tile_interleaved=hti, strict_reference_envelope=True)
+    with pytest.raises(AssertionError, match=message):
+        gemm_a16w16(a, b, user_kwargs=kw, layout="nt")
+
+
+def test_default_mode_has_no_cpu_path():
+    a = torch.empty(64, 480, dtype=torch.bfloat16)
+    b = _mat(480, 64, torch.bfloat16, True)
+    with pytest.raises(AssertionError, match="CUDA tensors only"):
+        gemm_a16w16(a, b)
+
+
+def test_dtype_and_shape_asserts():
+    a = torch.empty(8, 16, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError):
+        gemm_a16w16(a, torch.empty(16, 8, dtype=torch.float16), layout="nn")
+    with pytest.raises(AssertionError):
+        gemm_a16w16(a, torch.empty(12, 8, dtype=torch.bfloat16), layout="nn")
+    with pytest.raises(AssertionError):
+        gemm_a16w16(torch.empty(8, 16), torch.empty(16, 8), layout="nn")
+    with pytest.raises(ValueError, match="unsupported output dtype"):
+        gemm_a16w16(a, torch.empty(16, 8, dtype=torch.bfloat16), layout="nn", out_dtype=torch.float16)
+    with pytest.raises(AssertionError):  # out not contiguous
+        gemm_a16w16(a, torch.empty(16, 8, dtype=torch.bfloat16), out=torch.empty(8, 16, dtype=torch.bfloat16)[:, ::2], layout="nn")
+    with pytest.raises(AssertionError):  # bias length
+        gemm_a16w16(a, torch.empty(16, 8, dtype=torch.bfloat16), bias=torch.empty(7, dtype=torch.bfloat16), layout="nn")
+    with pytest.raises(ValueError, match="unknown gemm_a16w16 policy keys"):
+        P.from_user_kwargs({"tile_q": 3}, 8, 8, 8, "nt")
+
+
+def test_reference_policy_keys_are_accepted():
+    kw = dict(REF_KW, split_k=2, k_waves=1, use_half_tile_interleaved=True)
+    pol = P.from_user_kwargs(kw, 64, 64, 512, "nt")
+    assert pol.split_k == 2 and pol.tile_n in P.TILE_N_MENU
+    assert P.validate(pol, 64, 64, 512, "nt") is None
+    assert make_gemm_a16w16_param_and_validate(64, 64, 512, dict(kw, a_is_transposed=False, b_is_transposed=True)) is not None
+    assert make_gemm_a16w16_param_and_validate(64, 64, 512, {"tile_n": 48}) is None
+    assert make_gemm_a16w16_param_and_validate(64, 64, 512, {"tile_n": 256, "stages": 9}) is None
+
+
+def test_blackwell_policy_is_taken_literally():
+    pol = P.from_user_kwargs({"tile_n": 128, "stages": 3, "split_k": 5, "group_m": 2}, 4096, 4096, 4096, "nt")
+    assert (pol.tile_n, pol.stages, pol.split_k, pol.group_m, pol.swap_ab) == (128, 3, 5, 2, False)
+    pol = P.from_user_kwargs({"tile_n": 32, "swap_ab": True}, 32, 384, 7168, "nt")
+    assert pol.swap_ab and pol.split_k == 1
+
+
+def test_validate_rules():
+    assert P.validate(P.Policy(tile_n=32), 32, 384, 512, "nn") is not None  # N-contiguous B on a 32-wide tile
+    assert P.validate(P.Policy(tile_n=64), 32, 384, 512, "nn") is None
+    assert P.validate(P.Policy(tile_n=32, swap_ab=True), 32, 384, 512, "tn") is not None  # M-contiguous A after swap
+    assert P.validate(P.Policy(tile_n=256, stages=5), 512, 512, 512, "nt") is not None
+    assert P.validate(P.Policy(tile_n=256, stages=4), 512, 512, 512, "nt") is None
+    assert P.validate(P.Policy(tile_n=128, split_k=0), 512, 512, 512, "nt") is not None
+    for t in P.TILE_N_MENU:
+        assert P.smem_bytes(t, P.MAX_STAGES[t]) <= P.SMEM_LIMIT
+
+
+def test_heuristic_is_always_valid():
+    shapes = [(1, 5120, 2880), (3, 32, 256), (32, 384, 7168), (256, 512, 1024), (2048, 4096, 4096), (1000, 3000, 4100),
+              (16384, 28672, 8192), (16384, 3584, 8192), (65, 96, 192), (4096, 128, 6144), (8, 7168, 2048)]
+    for m, n, k in shapes:
+        for layout in ("nn", "nt", "tn", "tt"):
+            pol = P.heuristic(m, n, k, layout)
+            assert P.validate(pol, m, n, k, layout) is None, (m, n, k, layout, pol)
+
+
+def test_split_k_slices_cover_k_exactly_once():
+    for k in (1, 63, 64, 65, 1000, 4100, 7168):
+        for s in (1, 2, 3, 7, 8, 16, 32, 200):
+            sl = P.split_k_slices(k, s)
+            kb = (k + 63) // 64
+            assert len(sl) == min(s, kb)
+            assert all(n >= 1 for _, n in sl)
+            assert sl[0][0] == 0 and sum(n for _, n in sl) == kb
+            for (f0, n0), (f1, _) in zip(sl, sl[1:]):
+                assert f0 + n0 == f1
+
+
+@pytest.mark.parametrize("group", [0, 1, 3, 4, 8, 100])
+def test_raster_is_a_bijection(group):
+    for tp, tq in ((1, 1), (5, 7), (16, 16), (3, 64), (13, 2)):
+        seen = {P.raster(t, tp, tq, group) for t in range(tp * tq)}
+        assert seen == {(i, j) for i in range(tp) for j in range(tq)}
+
+
+def test_raster_groups_rows_like_group_m():
+    # group_m = 4 over 8x3 tiles: the first 12 tile ids cover rows 0..3 only, row index fastest
+    ids = [P.raster(t, 8, 3, 4) for t in range(12)]
+    assert {r for r, _ in ids} == {0, 1, 2, 3}
+    assert ids[:5] == [(0, 0), (1, 0), (2, 0), (3, 0), (0, 1)]
+
+
+def test_plan_query_on_cpu_tensors():
+    a = torch.empty(2048, 4096, dtype=torch.bfloat16)
+    b = torch.empty(4096, 4096, dtype=torch.bfloat16).t()
+    pl = plan(a, b, "nt", {"tile_n": 256, "group_m": 8})
+    assert (pl["tile_m"], pl["tile_n"], pl["tile_k"], pl["stages"]) == (128, 256, 64, 4)
+    assert pl["tiles_p"] * pl["tiles_q"] == 256 and pl["num_units"] == 256
+    assert pl["workspace_bytes"] == 0 and pl["tmem_cols"] == 512
+    assert pl["smem_bytes"] == P.smem_bytes(256, 4) <= P.SMEM_LIMIT
+    pl = plan(torch.empty(32, 7168, dtype=torch.bfloat16), torch.empty(384, 7168, dtype=torch.bfloat16).t(), "nt",
+              {"tile_n": 32, "swap_ab": True, "split_k": 16}, out_dtype=torch.float32)
+    assert pl["swap_ab"] == 1 and pl["tiles_p"] == 3 and pl["tiles_q"] == 1 and pl["num_units"] == 48
+    assert pl["partial_bytes"] == 48 * 128 * 32 * 4 and pl["counter_bytes"] == 256
+    # split_k larger than the number of K blocks is clamped
+    pl = plan(torch.empty(64, 100, dtype=torch.float16), torch.empty(100, 64, dtype=torch.float16), "nn", {"tile_n": 64, "split_k": 9})
+    assert pl["split_k"] == 2
+
+
+def test_plan_flags_operands_tma_cannot_describe():
+    # K = 4100 fp16 with +64 padding: a K-contiguous operand has an 8328-byte pitch (not a multiple of 16)
+    buf = torch.empty(1000 * 4164 + 256, dtype=torch.float16)
+    a = torch.as_strided(buf, (1000, 4100), (4164, 1), 128)
+    bbuf = torch.empty(4100 * 3064 + 256, dtype=torch.float16)
+    b = torch.as_strided(bbuf, (4100, 3000), (3064, 1), 128)
+    pl = plan(a, b, "nn", {"tile_n": 128}, out_dtype=torch.float32)
+    assert pl["a_repacked"] == 1
+    assert pl["repack_bytes"] >= 1000 * 4104 * 2
+    if b.data_ptr() % 16 == 0:
+        assert pl["b_repacked"] == 0
+
+
+def test_tuned_table_roundtrip(tmp_path):
+    import json
+    rec = {"arch": "sm_100a", "dtype": "bf16", "layout": "nt", "m": 32, "n": 384, "k": 7168,
+           "config": {"tile_n": 32, "swap_ab": True, "split_k": 16, "stages": 8}, "duration": 3.2, "tflops": 55.0}
+    other = dict(rec, arch="gfx950")
+    path = tmp_path / "t.jsonl"
+    path.write_text(json.dumps(other) + "\n" + json.dumps(rec) + "\n\n")
+    table = P.load_tuned(path)
+    assert list(table) == [("bf16", "nt", 32, 384, 7168)]
+    pol = P.from_user_kwargs(table[("bf16", "nt", 32, 384, 7168)], 32, 384, 7168, "nt")
+    assert pol.swap_ab and pol.split_k == 16 and pol.stages == 8
