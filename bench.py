@@ -188,6 +188,9 @@ class Workload:
         self.extra = {}
         big = name in ("c5", "c5_nshard", "c5_kshard")
         self.case = case = O.CONFIGS["c5" if big else name]
+        if args.policy:
+            import dataclasses
+            self.case = case = dataclasses.replace(case, user_kwargs=json.loads(args.policy))
         out_es = 4 if case.torch_out_dtype is torch.float32 else 2
         if big:
             # Synthetic N(0, 0.02) operands drawn on the device; C5's operands and output exceed L2 by themselves.
@@ -219,17 +222,17 @@ class Workload:
                 out = torch.empty((case.m, n1 - n0), dtype=torch.bfloat16, device=device)
 
                 def step():
-                    gemm_a16w16(a_full, b_loc, out, layout="nt")
+                    gemm_a16w16(a_full, b_loc, out, user_kwargs=case.user_kwargs, layout="nt")
 
                 self.per_rank_flops = 2.0 * case.m * (n1 - n0) * case.k
-                self.plan = plan(a_full, b_loc, "nt", {})
+                self.plan = plan(a_full, b_loc, "nt", case.user_kwargs)
                 self.launches_per_step = self.gemm_launches_per_step = 1
                 self.partition = (f"B sharded along N over {world} GPUs, no collective" if world > 1 else "whole GEMM on one GPU")
                 ins = [a_full, b_loc]
                 out_getter = lambda: out
             self.step = step
             self.algorithmic_bytes = None
-            e2e_kwargs, e2e_layout, bias = {}, "nt", None
+            e2e_kwargs, e2e_layout, bias = case.user_kwargs, "nt", None
         else:
             a, b, bias, *_ = O.build_inputs(case, device=device)
             per = a.untyped_storage().nbytes() + b.untyped_storage().nbytes() + case.m * case.n * out_es
@@ -411,7 +414,7 @@ def run_ours(args) -> dict:
             "partition": w.partition,
             "l2": w.rotation,
             "plan": {k: w.plan[k] for k in ("tile_m", "tile_n", "tile_k", "stages", "split_k", "swap_ab", "group_m", "grid",
-                                           "num_units", "a_repacked", "b_repacked")},
+                                           "num_units", "stream_k", "sk_tiles", "a_repacked", "b_repacked")},
         },
         "roofline": roofline,
         "clocks": clocks.summary(),
@@ -479,6 +482,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--chunks", type=int, default=4)
+    ap.add_argument("--policy", default=None, help="JSON dict of user_kwargs overriding the workload's policy")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-large", action="store_true")
     args = ap.parse_args()

@@ -71,6 +71,9 @@ class Plan(C.Structure):
         ("grid", C.c_int32),
         ("smem_bytes", C.c_int32),
         ("tmem_cols", C.c_int32),
+        ("stream_k", C.c_int32),
+        ("sk_tiles", C.c_int32),
+        ("sk_slots", C.c_int32),
         ("a_repacked", C.c_int32),
         ("b_repacked", C.c_int32),
         ("counter_bytes", C.c_uint64),
@@ -85,6 +88,9 @@ class Plan(C.Structure):
 
 EXPORTS = (
     "b200_gemm_a16w16",
+    "b200_gemm_prepare",
+    "b200_gemm_launch",
+    "b200_gemm_release",
     "b200_gemm_plan_query",
     "b200_gemm_workspace_bytes",
     "b200_gemm_num_variants",
@@ -121,6 +127,12 @@ def load() -> C.CDLL:
     lib = C.CDLL(str(path))
     lib.b200_gemm_a16w16.argtypes = [C.POINTER(Args), C.c_void_p]
     lib.b200_gemm_a16w16.restype = C.c_int
+    lib.b200_gemm_prepare.argtypes = [C.POINTER(Args), C.POINTER(C.c_void_p)]
+    lib.b200_gemm_prepare.restype = C.c_int
+    lib.b200_gemm_launch.argtypes = [C.c_void_p, C.c_void_p]
+    lib.b200_gemm_launch.restype = C.c_int
+    lib.b200_gemm_release.argtypes = [C.c_void_p]
+    lib.b200_gemm_release.restype = None
     lib.b200_gemm_plan_query.argtypes = [C.POINTER(Args), C.POINTER(Plan)]
     lib.b200_gemm_plan_query.restype = C.c_int
     lib.b200_gemm_workspace_bytes.argtypes = [C.POINTER(Args)]

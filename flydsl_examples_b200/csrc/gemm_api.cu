@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <new>
 
 #include "../../include/b200_gemm.h"
 #include "gemm_kernel.cuh"
@@ -14,6 +15,7 @@ namespace b200 {
 
 constexpr int kSmemLimit = 232448;  // 227 KB opt-in dynamic shared memory per CTA on sm_100
 constexpr int kMaxDevices = 16;
+constexpr uint64_t kCounterBytes = 1u << 20;  // fixed ticket region at the start of the workspace (262144 tiles)
 
 // ------------------------------------------------------------------ driver entry point (no -lcuda link needed)
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -178,8 +180,45 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
   int cap = pol.max_ctas > 0 ? pol.max_ctas : sms;
   pl.grid = pl.num_units < cap ? pl.num_units : cap;
 
-  pl.counter_bytes = pl.split_k > 1 ? round_up((uint64_t)tiles * 4, 256) : 0;
-  pl.partial_bytes = pl.split_k > 1 ? (uint64_t)pl.num_units * kTileP * pl.tile_n * 4 : 0;
+  // Stream-K: tiles that do not fill a whole wave of `cap` CTAs are cut into equal contiguous K spans, one per
+  // CTA; whole waves stay data-parallel. Spans shorter than kMinSpan K blocks are not worth a pipeline fill:
+  // borrow one full wave when there is one, else use fewer CTAs.
+  pl.stream_k = 0, pl.sk_tiles = 0, pl.sk_slots = 0;
+  if (pol.stream_k && tiles <= 0x7fffffffLL) {
+    constexpr int64_t kMinSpan = 4;
+    int64_t g = cap;
+    int64_t sk = tiles % g;
+    if (tiles < g) sk = tiles;
+    if (sk > 0 && sk * kb_total / g < kMinSpan) {
+      if (tiles > g) {
+        sk += g;
+      } else {
+        g = sk * kb_total / kMinSpan;
+        if (g > cap) g = cap;
+      }
+    }
+    if (sk > 0 && g >= 1 && sk * kb_total / g >= kMinSpan && sk * kb_total >= g) {
+      const int64_t span_min = sk * kb_total / g;
+      pl.stream_k = 1;
+      pl.split_k = 1;
+      pl.num_units = (int)tiles;
+      pl.sk_tiles = (int)sk;
+      pl.sk_slots = (int)((kb_total + span_min - 1) / span_min + 1);
+      pl.grid = (int)g;
+    } else if (sk == 0) {
+      pl.split_k = 1;  // whole waves only: plain data-parallel
+      pl.num_units = (int)tiles;
+      pl.grid = (int)(tiles < cap ? tiles : cap);
+    }
+  }
+
+  const bool tickets = pl.split_k > 1 || pl.sk_tiles > 0;
+  if (tickets && tiles > (int64_t)(kCounterBytes / 4)) return B200_GEMM_ERR_TOO_LARGE;
+  // The ticket region has a fixed size so that it never overlaps an area another call used for partial sums.
+  pl.counter_bytes = tickets ? kCounterBytes : 0;
+  pl.partial_bytes = pl.sk_tiles > 0 ? (uint64_t)pl.sk_tiles * pl.sk_slots * kTileP * pl.tile_n * 4
+                     : pl.split_k > 1 ? (uint64_t)pl.num_units * kTileP * pl.tile_n * 4
+                                      : 0;
   const uint64_t ra = pl.a_repacked ? round_up((uint64_t)a_rows * r->ra_ld * 2, 256) : 0;
   const uint64_t rb = pl.b_repacked ? round_up((uint64_t)b_rows * r->rb_ld * 2, 256) : 0;
   pl.repack_bytes = ra + rb;
@@ -237,7 +276,29 @@ static int set_cuda_error(cudaError_t e) {
   return B200_GEMM_ERR_LAUNCH;
 }
 
-static int launch(const b200_gemm_args* a, cudaStream_t stream) {
+// A fully resolved call: everything the launch needs, so that repeating it costs one (or up to three) kernel launches
+// and no host-side planning or tensor-map encoding.
+struct RepackJob {
+  const uint16_t* src;
+  uint16_t* dst;
+  long long src_ld, dst_ld;
+  int rows, cols, blocks;
+};
+
+}  // namespace b200
+
+struct b200_gemm_handle {
+  b200::GemmParams params;
+  b200::KernelFn fn;
+  int grid, smem_bytes, device;
+  int n_repack;
+  b200::RepackJob repack[2];
+  b200_gemm_plan plan;
+};
+
+namespace b200 {
+
+static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   DeviceInfo* dev = nullptr;
   int dev_id = 0;
   int rc = current_device_info(&dev, &dev_id);
@@ -251,30 +312,35 @@ static int launch(const b200_gemm_args* a, cudaStream_t stream) {
                                  (reinterpret_cast<uintptr_t>(a->workspace) & 255) != 0))
     return B200_GEMM_ERR_WORKSPACE;
   uint8_t* ws = reinterpret_cast<uint8_t*>(a->workspace);
+  h->plan = pl;
+  h->device = dev_id;
+  h->n_repack = 0;
 
   // Operands TMA cannot describe are first copied into an aligned image (same stream, ordered before the GEMM).
   const void* pa = a->a;
   const void* pb = a->b;
   int64_t lda = a->lda, ldb = a->ldb;
   const int a_mn = a->a_trans ? 1 : 0, b_mn = a->b_trans ? 0 : 1;
-  if (pl.a_repacked) {
-    const int rows = (int)(a_mn ? a->k : a->m), cols = (int)(a_mn ? a->m : a->k);
-    uint16_t* dst = reinterpret_cast<uint16_t*>(ws + r.off_repack_a);
+  auto add_repack = [&](const void* src, int64_t src_ld, uint64_t off, int64_t dst_ld, int rows, int cols) {
+    RepackJob& j = h->repack[h->n_repack++];
+    j.src = reinterpret_cast<const uint16_t*>(src);
+    j.dst = reinterpret_cast<uint16_t*>(ws + off);
+    j.src_ld = src_ld, j.dst_ld = dst_ld, j.rows = rows, j.cols = cols;
     const long long total = (long long)rows * ((cols + 7) / 8);
-    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    repack_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint16_t*>(a->a), a->lda, dst, r.ra_ld, rows, cols);
-    pa = dst, lda = r.ra_ld;
+    const long long want = (total + 255) / 256;
+    j.blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    return j.dst;
+  };
+  if (pl.a_repacked) {
+    pa = add_repack(a->a, a->lda, r.off_repack_a, r.ra_ld, (int)(a_mn ? a->k : a->m), (int)(a_mn ? a->m : a->k));
+    lda = r.ra_ld;
   }
   if (pl.b_repacked) {
-    const int rows = (int)(b_mn ? a->k : a->n), cols = (int)(b_mn ? a->n : a->k);
-    uint16_t* dst = reinterpret_cast<uint16_t*>(ws + r.off_repack_b);
-    const long long total = (long long)rows * ((cols + 7) / 8);
-    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    repack_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint16_t*>(a->b), a->ldb, dst, r.rb_ld, rows, cols);
-    pb = dst, ldb = r.rb_ld;
+    pb = add_repack(a->b, a->ldb, r.off_repack_b, r.rb_ld, (int)(b_mn ? a->k : a->n), (int)(b_mn ? a->n : a->k));
+    ldb = r.rb_ld;
   }
 
-  GemmParams p;
+  GemmParams& p = h->params;
   memset(&p, 0, sizeof(p));
   const void* u_ptr = pl.swap_ab ? pb : pa;
   const void* v_ptr = pl.swap_ab ? pa : pb;
@@ -294,6 +360,8 @@ static int launch(const b200_gemm_args* a, cudaStream_t stream) {
   p.kb_total = (int)((a->k + kTileK - 1) / kTileK);
   p.split_k = pl.split_k;
   p.num_units = pl.num_units;
+  p.sk_tiles = pl.sk_tiles;
+  p.sk_slots = pl.sk_slots;
   p.group_p = pl.group_m;
   p.swap_out = pl.swap_ab;
   p.out_dtype = a->out_dtype;
@@ -305,22 +373,33 @@ static int launch(const b200_gemm_args* a, cudaStream_t stream) {
 
   const Variant* var = find_variant(pl.tile_n, pl.cta_group);
   const int vi = (int)(var - kVariants);
-  KernelFn fn = var->fn[pl.stages];
+  h->fn = var->fn[pl.stages];
+  h->grid = pl.grid;
+  h->smem_bytes = pl.smem_bytes;
   {
     std::lock_guard<std::mutex> lock(g_dev_mutex);
     if (!dev->attr_set[vi][pl.stages]) {
-      cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes);
+      cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(h->fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           pl.smem_bytes);
       if (e != cudaSuccess) return set_cuda_error(e);
       dev->attr_set[vi][pl.stages] = true;
     }
   }
+  return 0;
+}
+
+static int run(const b200_gemm_handle* h, cudaStream_t stream) {
+  for (int i = 0; i < h->n_repack; ++i) {
+    const RepackJob& j = h->repack[i];
+    repack_rows_kernel<<<j.blocks, 256, 0, stream>>>(j.src, j.src_ld, j.dst, j.dst_ld, j.rows, j.cols);
+  }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(pl.grid, 1, 1);
+  cfg.gridDim = dim3(h->grid, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.dynamicSmemBytes = h->smem_bytes;
   cfg.stream = stream;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, fn, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, h->fn, h->params);
   if (e != cudaSuccess) return set_cuda_error(e);
   return 0;
 }
@@ -330,8 +409,32 @@ static int launch(const b200_gemm_args* a, cudaStream_t stream) {
 extern "C" {
 
 int b200_gemm_a16w16(const b200_gemm_args* args, void* cuda_stream) {
-  return b200::launch(args, reinterpret_cast<cudaStream_t>(cuda_stream));
+  b200_gemm_handle h;
+  const int rc = b200::prepare(args, &h);
+  if (rc) return rc;
+  return b200::run(&h, reinterpret_cast<cudaStream_t>(cuda_stream));
 }
+
+int b200_gemm_prepare(const b200_gemm_args* args, b200_gemm_handle** out) {
+  if (out == nullptr) return B200_GEMM_ERR_BAD_ARG;
+  *out = nullptr;
+  b200_gemm_handle* h = new (std::nothrow) b200_gemm_handle;
+  if (h == nullptr) return B200_GEMM_ERR_BAD_ARG;
+  const int rc = b200::prepare(args, h);
+  if (rc) {
+    delete h;
+    return rc;
+  }
+  *out = h;
+  return 0;
+}
+
+int b200_gemm_launch(const b200_gemm_handle* handle, void* cuda_stream) {
+  if (handle == nullptr) return B200_GEMM_ERR_BAD_ARG;
+  return b200::run(handle, reinterpret_cast<cudaStream_t>(cuda_stream));
+}
+
+void b200_gemm_release(b200_gemm_handle* handle) { delete handle; }
 
 int b200_gemm_plan_query(const b200_gemm_args* args, b200_gemm_plan* plan) {
   if (plan == nullptr) return B200_GEMM_ERR_BAD_ARG;

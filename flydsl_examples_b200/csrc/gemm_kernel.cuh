@@ -44,6 +44,8 @@ struct alignas(64) GemmParams {
   int kb_total;  // ceil(K / 64)
   int split_k;
   int num_units;
+  int sk_tiles;     // stream-K: the first sk_tiles tiles are cut into equal K spans over all CTAs (0 = off)
+  int sk_slots;     // stream-K: partial-tile slots reserved per tile (upper bound of contributors)
   int group_p;      // grouped rasterisation over tile rows of P (0 = off)
   int swap_out;     // 1: D^T is written (out[q*ldo + p]); bias indexed by p
   int out_dtype;    // 1 fp32, 2 bf16, 3 fp16
@@ -56,31 +58,86 @@ struct alignas(64) GemmParams {
   uint32_t u_kstep, v_kstep;  // start-address increment (16-byte units) per K=16 MMA inside a stage
 };
 
+// One piece of work of a CTA: K blocks [kb0, kb0+kbn) of output tile (tp, tq). When `partial`, the fp32 result goes to
+// slot `slot` of the workspace and the last of `n_contrib` contributors (ticket) reduces slots slot0..slot0+n_contrib-1.
 struct Unit {
-  int tile, slice, tp, tq, kb0, kbn;
+  int tile, tp, tq, kb0, kbn;
+  int partial, slot, slot0, n_contrib;
 };
 
-__device__ __forceinline__ Unit decode_unit(const GemmParams& p, int u) {
-  Unit w;
-  w.tile = u / p.split_k;
-  w.slice = u - w.tile * p.split_k;
+__device__ __forceinline__ void raster_tile(const GemmParams& p, int tile, int& tp, int& tq) {
   if (p.group_p > 0) {
     const int per_group = p.group_p * p.tiles_q;
-    const int g = w.tile / per_group;
+    const int g = tile / per_group;
     const int first = g * p.group_p;
     const int rows = min(p.tiles_p - first, p.group_p);
-    const int r = w.tile - g * per_group;
-    w.tp = first + r % rows;
-    w.tq = r / rows;
+    const int r = tile - g * per_group;
+    tp = first + r % rows;
+    tq = r / rows;
   } else {
-    w.tp = w.tile / p.tiles_q;
-    w.tq = w.tile - w.tp * p.tiles_q;
+    tp = tile / p.tiles_q;
+    tq = tile - tp * p.tiles_q;
   }
-  const int base = p.kb_total / p.split_k, rem = p.kb_total - base * p.split_k;
-  w.kb0 = w.slice * base + min(w.slice, rem);
-  w.kbn = base + (w.slice < rem ? 1 : 0);
-  return w;
 }
+
+// Walks the work of CTA blockIdx.x; all three roles run the same walk.
+//   split-K / data-parallel (sk_tiles == 0): units u = cta, cta+grid, ... ; unit = (tile, K slice).
+//   stream-K (sk_tiles > 0): first this CTA's equal share of the K blocks of tiles [0, sk_tiles) (a contiguous span
+//   that may cross tile boundaries), then whole tiles sk_tiles + cta, sk_tiles + cta + grid, ...
+struct WorkIter {
+  long long sk_cur, sk_end, sk_total;
+  int next_u;
+  __device__ __forceinline__ void init(const GemmParams& p) {
+    sk_total = (long long)p.sk_tiles * p.kb_total;
+    sk_cur = sk_total * blockIdx.x / gridDim.x;
+    sk_end = sk_total * (blockIdx.x + 1) / gridDim.x;
+    next_u = p.sk_tiles > 0 ? p.sk_tiles + (int)blockIdx.x : (int)blockIdx.x;
+  }
+  // CTA that owns stream-K iteration x: the largest b with floor(b * total / grid) <= x.
+  __device__ __forceinline__ int owner(long long x) const {
+    return (int)(((x + 1) * gridDim.x + sk_total - 1) / sk_total) - 1;
+  }
+  __device__ __forceinline__ bool next(const GemmParams& p, Unit& w) {
+    if (sk_cur < sk_end) {
+      w.tile = (int)(sk_cur / p.kb_total);
+      w.kb0 = (int)(sk_cur - (long long)w.tile * p.kb_total);
+      w.kbn = (int)min((long long)(p.kb_total - w.kb0), sk_end - sk_cur);
+      sk_cur += w.kbn;
+      raster_tile(p, w.tile, w.tp, w.tq);
+      w.partial = w.kbn != p.kb_total;
+      if (w.partial) {
+        const int first = owner((long long)w.tile * p.kb_total);
+        const int last = owner((long long)(w.tile + 1) * p.kb_total - 1);
+        w.n_contrib = last - first + 1;
+        w.slot0 = w.tile * p.sk_slots;
+        w.slot = w.slot0 + ((int)blockIdx.x - first);
+      }
+      return true;
+    }
+    if (p.sk_tiles > 0) {
+      if (next_u >= p.num_tiles) return false;
+      w.tile = next_u;
+      next_u += gridDim.x;
+      raster_tile(p, w.tile, w.tp, w.tq);
+      w.kb0 = 0, w.kbn = p.kb_total, w.partial = 0;
+      return true;
+    }
+    if (next_u >= p.num_units) return false;
+    const int u = next_u;
+    next_u += gridDim.x;
+    w.tile = u / p.split_k;
+    const int slice = u - w.tile * p.split_k;
+    raster_tile(p, w.tile, w.tp, w.tq);
+    const int base = p.kb_total / p.split_k, rem = p.kb_total - base * p.split_k;
+    w.kb0 = slice * base + min(slice, rem);
+    w.kbn = base + (slice < rem ? 1 : 0);
+    w.partial = p.split_k > 1;
+    w.n_contrib = p.split_k;
+    w.slot0 = w.tile * p.split_k;
+    w.slot = w.slot0 + slice;
+    return true;
+  }
+};
 
 template <int TILE_Q, int STAGES>
 struct SmemLayout {
@@ -233,8 +290,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       uint32_t phase = 0;
       int issued = 0;
       bool ok = true;
-      for (int u = blockIdx.x; ok && u < p.num_units; u += gridDim.x) {
-        const Unit w = decode_unit(p, u);
+      WorkIter wi;
+      wi.init(p);
+      Unit w;
+      while (ok && wi.next(p, w)) {
+        const int u = w.tile;
         const int p0 = w.tp * kTileP, q0 = w.tq * TILE_Q;
         for (int kb = w.kb0; kb < w.kb0 + w.kbn; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_s)) {
@@ -289,8 +349,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int u = blockIdx.x; ok && u < p.num_units; u += gridDim.x, ++it) {
-        const Unit w = decode_unit(p, u);
+      WorkIter wi;
+      wi.init(p);
+      Unit w;
+      for (; ok && wi.next(p, w); ++it) {
+        const int u = w.tile;
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(acce_bar(buf), acc_phase ^ 1u, abort_s)) {
@@ -330,13 +393,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
     const int row = quarter * 32 + lane;
     const int et = threadIdx.x - 64;  // 0..127
     int it = 0;
-    for (int u = blockIdx.x; u < p.num_units; u += gridDim.x, ++it) {
-      const Unit w = decode_unit(p, u);
+    WorkIter wi;
+    wi.init(p);
+    Unit w;
+    for (; wi.next(p, w); ++it) {
+      const int u = w.tile;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int prow = w.tp * kTileP + row;
       const int qbase = w.tq * TILE_Q;
-      const bool direct = (p.split_k == 1);
+      const bool direct = !w.partial;
 
       // Stage the bias slice of this tile (columns of D) while the main loop runs.
       float bias_p = 0.f;
@@ -360,7 +426,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       tc_fence_after();
       const uint32_t t_acc = tmem_base + buf * TILE_Q + (uint32_t(quarter * 32) << 16);
       float* part = nullptr;
-      if (!direct) part = p.partials + ((size_t)(w.tile * p.split_k + w.slice) * NCHUNK) * (kTileP * CW) + (size_t)row * CW;
+      if (!direct) part = p.partials + ((size_t)w.slot * NCHUNK) * (kTileP * CW) + (size_t)row * CW;
 
 #pragma unroll 1
       for (int c = 0; c < NCHUNK; ++c) {
@@ -393,7 +459,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         named_bar_sync(2, kEpiThreads);
         if (et == 0) {
           const int t = atomicAdd(p.tickets + w.tile, 1);
-          const int last = (t == p.split_k - 1) ? 1 : 0;
+          const int last = (t == w.n_contrib - 1) ? 1 : 0;
           if (last) p.tickets[w.tile] = 0;  // self-cleaning: nobody else touches it until the next launch
           *last_s = last;
         }
@@ -401,13 +467,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         const int last = *last_s;
         if (last) {
           __threadfence();
-          const float* tp0 = p.partials + ((size_t)w.tile * p.split_k * NCHUNK) * (kTileP * CW) + (size_t)row * CW;
+          const float* tp0 = p.partials + ((size_t)w.slot0 * NCHUNK) * (kTileP * CW) + (size_t)row * CW;
 #pragma unroll 1
           for (int c = 0; c < NCHUNK; ++c) {
             float v[CW];
 #pragma unroll
             for (int i = 0; i < CW; ++i) v[i] = 0.f;
-            for (int s = 0; s < p.split_k; ++s) {
+            for (int s = 0; s < w.n_contrib; ++s) {
               const float4* src = reinterpret_cast<const float4*>(tp0 + ((size_t)s * NCHUNK + c) * (kTileP * CW));
 #pragma unroll
               for (int i = 0; i < CW; i += 4) {

@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import ctypes as C
 import threading
+from collections import OrderedDict
 from typing import Optional
 
 import torch
@@ -39,17 +40,19 @@ class _Workspace:
     4-word status block kernels write when a bounded wait gives up. Grows on demand, never shrinks.
     Takes the place of get_split_k_buffers (kernels/gemm_a16w16_gfx950.py:1277-1281)."""
 
-    __slots__ = ("buf", "status")
+    __slots__ = ("buf", "status", "generation")
 
     def __init__(self, device: torch.device):
         self.buf = None
+        self.generation = 0
         self.status = torch.zeros(_STATUS_WORDS, dtype=torch.int32, device=device)
 
     def ensure(self, nbytes: int, device: torch.device, stream: torch.cuda.Stream) -> None:
         if self.buf is None or self.buf.numel() < nbytes:
             with torch.cuda.stream(stream):
                 # Zero-filled: the ticket area must start at zero; kernels leave it zero.
-                self.buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+                self.buf = torch.zeros(max(nbytes, 4 << 20), dtype=torch.uint8, device=device)
+            self.generation += 1  # prepared launches that point into the old buffer are stale
 
 
 def _workspace_for(device: torch.device, stream: torch.cuda.Stream) -> _Workspace:
@@ -202,6 +205,52 @@ def _fill_args(a, b, out, bias, pol: _policy.Policy, a_t: bool, b_t: bool) -> _l
     return args
 
 
+class _Prepared:
+    """A resolved call kept for reuse: the C handle plus what it depends on."""
+
+    __slots__ = ("handle", "ws", "ws_gen", "dev", "n")
+
+    def __init__(self, handle, ws, dev, n):
+        self.handle, self.ws, self.ws_gen, self.dev, self.n = handle, ws, ws.generation, dev, n
+
+
+_PREPARED_MAX = 2048
+_prepared: "OrderedDict[tuple, _Prepared]" = OrderedDict()
+_prepared_lock = threading.Lock()
+
+
+def _call_key(a, b, out, bias, kw_key, stream_ptr, layout, out_dtype):
+    return (
+        a.data_ptr(), a.shape, a.stride(), a.dtype,
+        b.data_ptr(), b.shape, b.stride(),
+        out.data_ptr(), out.shape, out.dtype,
+        None if bias is None else (bias.data_ptr(), bias.shape, bias.stride(), bias.dtype),
+        kw_key, stream_ptr, layout, out_dtype, a.device.index, b.dtype, b.device.index, out.device.index,
+    )
+
+
+def _remember(key, ent: _Prepared) -> None:
+    with _prepared_lock:
+        old = _prepared.pop(key, None)
+        _prepared[key] = ent
+        evicted = [old] if old is not None else []
+        while len(_prepared) > _PREPARED_MAX:
+            evicted.append(_prepared.popitem(last=False)[1])
+    lib = _lib.load()
+    for e in evicted:
+        lib.b200_gemm_release(e.handle)
+
+
+def clear_prepared_calls() -> None:
+    """Drop every cached launch handle (tests; or after freeing the tensors they point at in bulk)."""
+    with _prepared_lock:
+        items = list(_prepared.values())
+        _prepared.clear()
+    lib = _lib.load()
+    for e in items:
+        lib.b200_gemm_release(e.handle)
+
+
 def gemm_a16w16(
     a: torch.Tensor,
     b: torch.Tensor,
@@ -217,7 +266,29 @@ def gemm_a16w16(
     Logical shapes never change with `layout`; each character only states which dimension of that operand is
     contiguous ('n' row-major, 't' column-major), exactly as in the reference. `out` may be any contiguous
     tensor with M*N elements; the returned tensor shares its storage. Asynchronous on `stream`.
+
+    A call whose tensors (address, shape, strides, dtype), policy and stream were seen before reuses its resolved
+    launch: validation, planning and tensor-map encoding are done once per distinct call.
     """
+    # ---- repeat of a call seen before: one dictionary lookup and one C call
+    if out is not None and a.is_cuda:
+        stream_ptr = (torch.cuda.current_stream(a.device) if stream is None else stream).cuda_stream
+        kw_key = tuple(sorted(user_kwargs.items())) if user_kwargs else ()
+        key = _call_key(a, b, out, bias, kw_key, stream_ptr, layout, out_dtype)
+        ent = _prepared.get(key)
+        if ent is not None and ent.ws_gen == ent.ws.generation:
+            if torch.cuda.current_device() == ent.dev:
+                rc = _lib.load().b200_gemm_launch(ent.handle, stream_ptr)
+            else:
+                with torch.cuda.device(ent.dev):
+                    rc = _lib.load().b200_gemm_launch(ent.handle, stream_ptr)
+            if rc != 0:
+                raise RuntimeError(f"b200_gemm_launch failed ({rc}): {_lib.strerror(rc)}")
+            return out.view(-1, ent.n)
+    else:
+        key = None
+
+    # ---- first time: validate (same contract as the reference), plan, prepare, launch
     layout = layout.lower()
     if layout not in ("nn", "nt", "tn", "tt"):
         raise ValueError(f"unsupported GEMM layout: {layout!r}; expected 'nn', 'nt', 'tn', or 'tt'")
@@ -240,6 +311,7 @@ def gemm_a16w16(
         out_dtype = a.dtype if out is None else out.dtype
     if out_dtype not in (a.dtype, torch.float32):
         raise ValueError(f"unsupported output dtype {out_dtype}; expected {a.dtype} or torch.float32")
+    out_in = out
     if out is None:
         out = torch.empty((m, n), dtype=out_dtype, device=device)
     else:
@@ -249,6 +321,7 @@ def gemm_a16w16(
     out = out.view(-1, n)
     assert out.shape[0] == m
 
+    bias_in = bias
     if bias is not None:
         if not bias.is_contiguous():
             bias = bias.contiguous()
@@ -280,16 +353,27 @@ def gemm_a16w16(
     args = _fill_args(a, b, out, bias, pol, a_t, b_t)
     lib = _lib.load()
     ws = _workspace_for(device, stream)
-    with torch.cuda.device(device):
+    dev_index = device.index if device.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(dev_index):
         need = lib.b200_gemm_workspace_bytes(C.byref(args))
         if need:
             ws.ensure(need, device, stream)
             args.workspace = ws.buf.data_ptr()
             args.workspace_bytes = ws.buf.numel()
         args.status = ws.status.data_ptr()
-        rc = lib.b200_gemm_a16w16(C.byref(args), C.c_void_p(stream.cuda_stream))
+        handle = C.c_void_p()
+        rc = lib.b200_gemm_prepare(C.byref(args), C.byref(handle))
+        if rc != 0:
+            raise RuntimeError(f"b200_gemm_prepare failed ({rc}): {_lib.strerror(rc)}")
+        rc = lib.b200_gemm_launch(handle, C.c_void_p(stream.cuda_stream))
     if rc != 0:
-        raise RuntimeError(f"b200_gemm_a16w16 failed ({rc}): {_lib.strerror(rc)}")
+        lib.b200_gemm_release(handle)
+        raise RuntimeError(f"b200_gemm_launch failed ({rc}): {_lib.strerror(rc)}")
+    # Remember the launch only when it describes the caller's own tensors (a made-contiguous bias is a temporary).
+    if key is not None and bias is bias_in and out_in is not None:
+        _remember(key, _Prepared(handle, ws, dev_index, n))
+    else:
+        lib.b200_gemm_release(handle)
     return out
 
 

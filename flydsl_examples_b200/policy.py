@@ -78,6 +78,51 @@ def raster(tile: int, tiles_p: int, tiles_q: int, group: int) -> tuple[int, int]
     return tile // tiles_q, tile % tiles_q
 
 
+def stream_k_plan(tiles: int, kb_total: int, cap: int, min_span: int = 4) -> tuple[int, int, int]:
+    """(grid, sk_tiles, sk_slots) of the stream-K schedule; sk_tiles == 0 means plain data-parallel.
+    The tiles that do not fill a whole wave of `cap` CTAs are cut into equal contiguous spans of K blocks, one
+    span per CTA; if a span would be shorter than `min_span` blocks one full wave is added to the cut region, or,
+    with less than one wave of tiles, fewer CTAs are used. Mirrors the planner in csrc/gemm_api.cu."""
+    g = cap
+    sk = tiles % g if tiles >= g else tiles
+    if sk > 0 and sk * kb_total // g < min_span:
+        if tiles > g:
+            sk += g
+        else:
+            g = min(cap, sk * kb_total // min_span)
+    if sk > 0 and g >= 1 and sk * kb_total // g >= min_span:
+        span_min = sk * kb_total // g
+        return g, sk, (kb_total + span_min - 1) // span_min + 1
+    return min(tiles, cap), 0, 0
+
+
+def stream_k_walk(cta: int, grid: int, tiles: int, kb_total: int, sk_tiles: int) -> list[dict]:
+    """Work items of one CTA, in order, exactly as the device-side walk produces them: first its span of the
+    stream-K region (may cross tile boundaries), then whole tiles sk_tiles + cta, + grid, ..."""
+    total = sk_tiles * kb_total
+
+    def owner(x: int) -> int:
+        return ((x + 1) * grid + total - 1) // total - 1
+
+    items = []
+    cur, end = total * cta // grid, total * (cta + 1) // grid
+    while cur < end:
+        tile = cur // kb_total
+        kb0 = cur - tile * kb_total
+        kbn = min(kb_total - kb0, end - cur)
+        item = {"tile": tile, "kb0": kb0, "kbn": kbn, "partial": kbn != kb_total}
+        if item["partial"]:
+            first, last = owner(tile * kb_total), owner((tile + 1) * kb_total - 1)
+            item.update(n_contrib=last - first + 1, ordinal=cta - first)
+        items.append(item)
+        cur += kbn
+    t = sk_tiles + cta
+    while sk_tiles > 0 and t < tiles:
+        items.append({"tile": t, "kb0": 0, "kbn": kb_total, "partial": False})
+        t += grid
+    return items
+
+
 def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
     """Return None when the policy is runnable for this problem, else the reason."""
     if pol.tile_n not in TILE_N_MENU:

@@ -31,6 +31,9 @@ extern "C" {
 #define B200_GEMM_ERR_DRIVER (-6)         /* driver entry point not found                           */
 #define B200_GEMM_ERR_TOO_LARGE (-7)      /* size beyond a stated fixed limit                       */
 
+/* size of the ticket region at the start of a workspace */
+#define B200_GEMM_COUNTER_BYTES (1u << 20)
+
 /* split-K reduction modes */
 #define B200_GEMM_SPLIT_TICKET 0 /* fp32 partial tiles in the workspace; the last-arriving CTA of a tile sums them in
                                     slice order, adds bias and casts once (deterministic; never waits)            */
@@ -68,8 +71,9 @@ typedef struct b200_gemm_args {
   int32_t in_dtype;  /* B200_GEMM_DTYPE_BF16 or _FP16                                                      */
   int32_t out_dtype; /* in_dtype or B200_GEMM_DTYPE_FP32                                                   */
   b200_gemm_policy policy;
-  void* workspace; /* device scratch of at least b200_gemm_workspace_bytes(); its first counter_bytes must be zero
-                      before the first call and are left zero by every call (self-cleaning tickets)             */
+  void* workspace; /* device scratch of at least b200_gemm_workspace_bytes(), 256-byte aligned; its first
+                      B200_GEMM_COUNTER_BYTES hold the split-K / stream-K tickets: zero them once before the first
+                      call; every call leaves them zero again (self-cleaning)                                   */
   uint64_t workspace_bytes;
   int32_t* status; /* device int32[4], or NULL. Written only when a bounded wait inside a kernel gave up:
                       [0]=error code (1), [1]=CTA, [2]=role, [3]=unit                                         */
@@ -81,6 +85,7 @@ typedef struct b200_gemm_plan {
   int32_t tiles_p, tiles_q; /* tile grid over (128-row operand, tile_n operand)                              */
   int32_t num_units, grid;  /* work units (tile x K-slice) and persistent CTAs                               */
   int32_t smem_bytes, tmem_cols;
+  int32_t stream_k, sk_tiles, sk_slots; /* stream-K on; tiles cut into K spans; partial slots reserved per such tile */
   int32_t a_repacked, b_repacked; /* 1 when the operand is not TMA-encodable (base or pitch not 16-byte aligned)
                                      and is first copied into an aligned scratch image in the workspace        */
   uint64_t counter_bytes, partial_bytes, repack_bytes, workspace_bytes;
@@ -90,6 +95,17 @@ typedef struct b200_gemm_plan {
  * Replaces: gemm_a16w16 -> run_cached -> gemm_a16w16_gfx950 launch
  * (kernels/gemm_a16w16_gfx950.py:1434-1440, kernels/common.py:7-39). */
 int b200_gemm_a16w16(const b200_gemm_args* args, void* cuda_stream);
+
+/* Plan once, launch many times. b200_gemm_prepare does all host-side work of a call (validation, plan, tensor maps;
+ * host memory only) and returns an opaque handle; b200_gemm_launch enqueues the kernels of that call on a stream of
+ * the device that was current at prepare time; b200_gemm_release frees the handle. The handle stays valid while the
+ * buffers named in `args` (operands, output, bias, workspace, status) stay where they are.
+ * Replaces the per-policy compiled-kernel cache of run_cached (kernels/common.py:7-39) keyed on the constexpr
+ * param: here the cached object is the resolved launch, not compiled code. */
+typedef struct b200_gemm_handle b200_gemm_handle;
+int b200_gemm_prepare(const b200_gemm_args* args, b200_gemm_handle** handle);
+int b200_gemm_launch(const b200_gemm_handle* handle, void* cuda_stream);
+void b200_gemm_release(b200_gemm_handle* handle);
 
 /* Resolve the policy for these arguments without launching.
  * Replaces: make_gemm_a16w16_param_and_validate + assert_no_k_tail

@@ -54,7 +54,8 @@ def test_config1_bf16_nt_256x512x1024():
     run_case(O.CONFIGS["c1"], repeats=3)
 
 
-@pytest.mark.parametrize("kw", [{}, {"tile_n": 256, "group_m": 8}, {"tile_n": 128, "stages": 6}])
+@pytest.mark.parametrize("kw", [{}, {"tile_n": 256, "group_m": 8}, {"tile_n": 128, "stages": 6}, {"tile_n": 256, "stream_k": True},
+                                {"tile_n": 128, "stream_k": True, "group_m": 4}])
 def test_config2_bf16_nt_bias(kw):
     case = O.CONFIGS["c2"]
     run_case(O.Case(**{**case.__dict__, "user_kwargs": kw}))
@@ -80,7 +81,7 @@ def _c4_reference():
 
 
 @pytest.mark.parametrize("layout", LAYOUTS)
-@pytest.mark.parametrize("kw", [{}, {"tile_n": 128, "split_k": 2}])
+@pytest.mark.parametrize("kw", [{}, {"tile_n": 128, "split_k": 2}, {"tile_n": 256, "stream_k": True}])
 def test_config4_fp16_padded_offset_ktail(layout, kw):
     case = O.CONFIGS[f"c4_{layout}"]
     a_l, b_l, bias_l, ref = _c4_reference()
@@ -155,6 +156,37 @@ def test_split_k_shapes(layout, dtype, idx):
     for out_dtype in (None, "fp32"):
         run_case(O.Case("split", dtype, layout, m, n, k, seed=200 + idx, bias_std=0.5, out_dtype=out_dtype, user_kwargs=kw),
                  repeats=2, prefill="randn")
+
+
+STREAM_K = [  # shapes whose tile count is not a multiple of the SM count, or smaller than it
+    (2048, 4096, 4096, {"tile_n": 256, "stream_k": True}),                 # 256 tiles: 108 cut into spans
+    (1000, 3000, 4100, {"tile_n": 256, "stream_k": True}),                 # 96 tiles: all cut
+    (1000, 3000, 4100, {"tile_n": 128, "stream_k": True, "group_m": 2}),
+    (32, 384, 7168, {"tile_n": 32, "swap_ab": True, "stream_k": True}),    # 3 tiles over 84 CTAs
+    (4096, 4736, 512, {"tile_n": 128, "stream_k": True}),                  # remainder wave with short K: borrows a wave
+    (129, 136, 1536, {"tile_n": 64, "stream_k": True}),
+    (640, 640, 8192, {"tile_n": 128, "stream_k": True}),
+    (1, 5120, 2880, {"tile_n": 64, "stream_k": True}),
+]
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("idx", range(len(STREAM_K)))
+def test_stream_k_shapes(dtype, idx):
+    m, n, k, kw = STREAM_K[idx]
+    layouts = ("nt",) if kw["tile_n"] < 64 else (("nt", "nn") if m * n * k > 1 << 32 else LAYOUTS)
+    for layout in layouts:
+        for out_dtype in (None, "fp32"):
+            run_case(O.Case("streamk", dtype, layout, m, n, k, seed=300 + idx, bias_std=0.5, out_dtype=out_dtype, user_kwargs=kw),
+                     repeats=2, prefill="randn")
+
+
+def test_stream_k_is_deterministic():
+    case = O.Case("sk_det", "bf16", "nt", 1000, 3000, 4100, seed=5, bias_std=0.5, user_kwargs={"tile_n": 256, "stream_k": True})
+    a, b, bias, *_ = O.build_inputs(case, device=DEV)
+    outs = [gemm_a16w16(a, b, bias=bias, user_kwargs=case.user_kwargs, layout="nt").clone() for _ in range(4)]
+    check_status()
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
 
 
 @pytest.mark.parametrize("layout", LAYOUTS)
@@ -301,6 +333,34 @@ def test_repeated_calls_leave_tickets_clean():
     run_case(case, repeats=5, prefill="randn")
     # a different split-K shape right after, on the same workspace
     run_case(O.Case("repeat2", "fp16", "nt", 100, 700, 1000, seed=42, user_kwargs={"tile_n": 128, "split_k": 4}), repeats=2)
+
+
+def test_prepared_call_cache_tracks_workspace_growth_and_new_tensors():
+    from flydsl_examples_b200 import gemm_a16w16 as G
+
+    G.clear_prepared_calls()
+    case = O.Case("cache", "bf16", "nt", 130, 200, 2048, seed=51, bias_std=0.5, out_dtype="fp32", user_kwargs={"tile_n": 64, "split_k": 4})
+    a, b, bias, a_l, b_l, bias_l = O.build_inputs(case, device=DEV)
+    ref = O.reference_matmul(a_l, b_l, bias_l, torch.float32)
+    out = torch.empty((130, 200), dtype=torch.float32, device=DEV)
+    for _ in range(3):  # first call prepares, the next two reuse the handle
+        out.fill_(float("nan"))
+        gemm_a16w16(a, b, out, bias=bias, user_kwargs=case.user_kwargs, layout="nt")
+        check_status()
+        O.assert_close(out, ref, case.k, "cached call")
+    assert len(G._prepared) == 1
+    # a call that needs a much larger workspace makes it grow; the old handle must not be reused with the stale pointer
+    big = O.Case("cache_big", "bf16", "nt", 1024, 2048, 8192, seed=52, out_dtype="fp32", user_kwargs={"tile_n": 128, "split_k": 16})
+    run_case(big)
+    out.fill_(float("nan"))
+    gemm_a16w16(a, b, out, bias=bias, user_kwargs=case.user_kwargs, layout="nt")
+    check_status()
+    O.assert_close(out, ref, case.k, "after workspace growth")
+    # same storage, new contents: the cached launch reads the new data
+    a.copy_((a_l * 2).to(DEV))
+    gemm_a16w16(a, b, out, bias=bias, user_kwargs=case.user_kwargs, layout="nt")
+    check_status()
+    O.assert_close(out, O.reference_matmul(a_l * 2, b_l, bias_l, torch.float32), case.k, "new contents")
 
 
 def test_zero_sized_and_k_zero():

@@ -159,7 +159,7 @@ def test_plan_query_on_cpu_tensors():
     pl = plan(torch.empty(32, 7168, dtype=torch.bfloat16), torch.empty(384, 7168, dtype=torch.bfloat16).t(), "nt",
               {"tile_n": 32, "swap_ab": True, "split_k": 16}, out_dtype=torch.float32)
     assert pl["swap_ab"] == 1 and pl["tiles_p"] == 3 and pl["tiles_q"] == 1 and pl["num_units"] == 48
-    assert pl["partial_bytes"] == 48 * 128 * 32 * 4 and pl["counter_bytes"] == 256
+    assert pl["partial_bytes"] == 48 * 128 * 32 * 4 and pl["counter_bytes"] == 1 << 20
     # split_k larger than the number of K blocks is clamped
     pl = plan(torch.empty(64, 100, dtype=torch.float16), torch.empty(100, 64, dtype=torch.float16), "nn", {"tile_n": 64, "split_k": 9})
     assert pl["split_k"] == 2
@@ -189,3 +189,46 @@ def test_tuned_table_roundtrip(tmp_path):
     assert list(table) == [("bf16", "nt", 32, 384, 7168)]
     pol = P.from_user_kwargs(table[("bf16", "nt", 32, 384, 7168)], 32, 384, 7168, "nt")
     assert pol.swap_ab and pol.split_k == 16 and pol.stages == 8
+
+
+@pytest.mark.parametrize(("tiles", "kb", "cap"), [(256, 64, 148), (96, 65, 148), (3, 112, 148), (1792, 128, 148), (149, 2, 148),
+                                                  (148, 64, 148), (1, 1000, 148), (300, 5, 148), (7, 3, 148), (14336, 128, 148)])
+def test_stream_k_walk_covers_every_k_block_once(tiles, kb, cap):
+    grid, sk_tiles, sk_slots = P.stream_k_plan(tiles, kb, cap)
+    if sk_tiles == 0:
+        assert tiles % cap == 0 or tiles * kb < 4 * 1 or (tiles % cap) * kb // cap < 4
+        return
+    assert 1 <= grid <= cap and sk_tiles <= tiles
+    seen = {}
+    contrib = {}
+    for cta in range(grid):
+        items = P.stream_k_walk(cta, grid, tiles, kb, sk_tiles)
+        assert items, "every CTA gets work"
+        for it in items:
+            for blk in range(it["kb0"], it["kb0"] + it["kbn"]):
+                assert (it["tile"], blk) not in seen
+                seen[(it["tile"], blk)] = cta
+            if it["partial"]:
+                contrib.setdefault(it["tile"], []).append((it["ordinal"], it["n_contrib"], cta))
+    assert len(seen) == tiles * kb
+    for tile, lst in contrib.items():
+        n = lst[0][1]
+        assert all(x[1] == n for x in lst) and n <= sk_slots
+        assert sorted(x[0] for x in lst) == list(range(n))  # ordinals are exactly 0..n-1: the ticket completes
+    # spans are balanced to within one K block
+    loads = [sum(it["kbn"] for it in P.stream_k_walk(c, grid, tiles, kb, sk_tiles) if it["tile"] < sk_tiles) for c in range(grid)]
+    assert max(loads) - min(loads) <= 1
+
+
+def test_stream_k_plan_matches_the_library():
+    cases = [((2048, 4096, 4096), 256), ((1000, 3000, 4100), 256), ((16384, 3584, 8192), 256), ((32, 384, 7168), 64), ((4096, 4736, 512), 128)]
+    for (m, n, k), tile_n in cases:
+        a = torch.empty(m, k, dtype=torch.bfloat16)
+        b = torch.empty(n, k, dtype=torch.bfloat16).t()
+        pl = plan(a, b, "nt", {"tile_n": tile_n, "stream_k": True})
+        tiles = pl["tiles_p"] * pl["tiles_q"]
+        grid, sk_tiles, sk_slots = P.stream_k_plan(tiles, (k + 63) // 64, 148)
+        assert (pl["grid"], pl["sk_tiles"], pl["sk_slots"]) == (grid, sk_tiles, sk_slots), (m, n, k)
+        assert pl["stream_k"] == (1 if sk_tiles else 0)
+        if sk_tiles:
+            assert pl["partial_bytes"] == sk_tiles * sk_slots * 128 * tile_n * 4 and pl["counter_bytes"] == 1 << 20
