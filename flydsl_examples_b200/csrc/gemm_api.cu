@@ -44,24 +44,25 @@ struct Variant {
   KernelFn fn[13];  // indexed by stage count (2..12)
 };
 
-template <int TILE_Q, int S>
+template <int TILE_Q, int S, int CG>
 constexpr KernelFn kfn() {
-  if constexpr (SmemLayout<TILE_Q, S>::kDynBytes <= kSmemLimit)
-    return gemm_a16w16_sm100_kernel<TILE_Q, S>;
+  if constexpr (SmemLayout<TILE_Q, S, CG>::kDynBytes <= kSmemLimit)
+    return gemm_a16w16_sm100_kernel<TILE_Q, S, CG>;
   else
     return nullptr;
 }
 
-#define B200_VARIANT(TQ, MAXS)                                                                                    \
+#define B200_VARIANT(TQ, CG, MAXS)                                                                                \
   {                                                                                                               \
-    TQ, 1, MAXS, {                                                                                                \
-      nullptr, nullptr, kfn<TQ, 2>(), kfn<TQ, 3>(), kfn<TQ, 4>(), kfn<TQ, 5>(), kfn<TQ, 6>(), nullptr,            \
-          kfn<TQ, 8>(), nullptr, kfn<TQ, 10>(), nullptr, nullptr                                                  \
+    TQ, CG, MAXS, {                                                                                               \
+      nullptr, nullptr, kfn<TQ, 2, CG>(), kfn<TQ, 3, CG>(), kfn<TQ, 4, CG>(), kfn<TQ, 5, CG>(), kfn<TQ, 6, CG>(), \
+          nullptr, kfn<TQ, 8, CG>(), nullptr, kfn<TQ, 10, CG>(), nullptr, nullptr                                 \
     }                                                                                                             \
   }
 
 static const Variant kVariants[] = {
-    B200_VARIANT(16, 10), B200_VARIANT(32, 10), B200_VARIANT(64, 8), B200_VARIANT(128, 6), B200_VARIANT(256, 4),
+    B200_VARIANT(16, 1, 10), B200_VARIANT(32, 1, 10), B200_VARIANT(64, 1, 8), B200_VARIANT(128, 1, 6),
+    B200_VARIANT(256, 1, 4), B200_VARIANT(128, 2, 8), B200_VARIANT(256, 2, 6),
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -71,8 +72,8 @@ static const Variant* find_variant(int tile_q, int cta_group) {
   return nullptr;
 }
 
-static int dyn_smem_bytes(int tile_q, int stages) {
-  return stages * (kUStageBytes + tile_q * kTileK * 2) + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024;
+static int dyn_smem_bytes(int tile_q, int stages, int cta_group) {
+  return stages * (kUStageBytes + (tile_q / cta_group) * kTileK * 2) + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024;
 }
 
 struct DeviceInfo {
@@ -129,6 +130,7 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
   b200_gemm_plan& pl = r->plan;
   memset(&pl, 0, sizeof(pl));
   pl.cta_group = pol.cta_group == 0 ? 1 : pol.cta_group;
+  if (pl.cta_group != 1 && pl.cta_group != 2) return B200_GEMM_ERR_BAD_POLICY;
   pl.swap_ab = pol.swap_ab ? 1 : 0;
   pl.tile_m = kTileP * pl.cta_group;
   pl.tile_n = pol.tile_n;
@@ -155,7 +157,7 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
     r->P = (int)a->n, r->Q = (int)a->m;
     r->u_mn = b_mn, r->v_mn = a_mn;
   }
-  if (r->v_mn && pl.tile_n < 64) return B200_GEMM_ERR_BAD_POLICY;  // an MN-major box is 64 elements wide
+  if (r->v_mn && pl.tile_n / pl.cta_group < 64) return B200_GEMM_ERR_BAD_POLICY;  // an MN-major box is 64 elements wide
 
   pl.tiles_p = (r->P + pl.tile_m - 1) / pl.tile_m;
   pl.tiles_q = (r->Q + pl.tile_n - 1) / pl.tile_n;
@@ -171,31 +173,33 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
   while (stages >= 2 && (var->fn[stages] == nullptr)) --stages;
   if (stages < 2) return B200_GEMM_ERR_BAD_POLICY;
   pl.stages = stages;
-  pl.smem_bytes = dyn_smem_bytes(pl.tile_n, stages);
+  pl.smem_bytes = dyn_smem_bytes(pl.tile_n, stages, pl.cta_group);
   pl.tmem_cols = 2 * pl.tile_n < 32 ? 32 : 2 * pl.tile_n;
 
   int sms = sm_count_hint;
   if (need_sm_count && sms <= 0) return B200_GEMM_ERR_LAUNCH;
   if (sms <= 0) sms = 148;
-  int cap = pol.max_ctas > 0 ? pol.max_ctas : sms;
-  pl.grid = pl.num_units < cap ? pl.num_units : cap;
+  // `cap` counts schedulable walkers: CTAs, or CTA pairs when two CTAs share a tile.
+  int cap = (pol.max_ctas > 0 ? pol.max_ctas : sms) / pl.cta_group;
+  if (cap < 1) cap = 1;
+  pl.grid = (pl.num_units < cap ? pl.num_units : cap) * pl.cta_group;
 
   // Stream-K: tiles that do not fill a whole wave of `cap` CTAs are cut into equal contiguous K spans, one per
-  // CTA; whole waves stay data-parallel. Spans shorter than kMinSpan K blocks are not worth a pipeline fill:
-  // borrow one full wave when there is one, else use fewer CTAs.
+  // CTA; whole waves stay data-parallel. A remainder that would give spans shorter than half a tile (many
+  // contributors per tile) borrows one full wave; with less than one wave of tiles, spans shorter than kMinSpan K
+  // blocks are not worth a pipeline fill and fewer CTAs are used.
   pl.stream_k = 0, pl.sk_tiles = 0, pl.sk_slots = 0;
   if (pol.stream_k && tiles <= 0x7fffffffLL) {
     constexpr int64_t kMinSpan = 4;
     int64_t g = cap;
     int64_t sk = tiles % g;
     if (tiles < g) sk = tiles;
-    if (sk > 0 && sk * kb_total / g < kMinSpan) {
-      if (tiles > g) {
-        sk += g;
-      } else {
-        g = sk * kb_total / kMinSpan;
-        if (g > cap) g = cap;
-      }
+    const int64_t borrow_below = kb_total / 2 > kMinSpan ? kb_total / 2 : kMinSpan;
+    if (sk > 0 && tiles > g && sk * kb_total / g < borrow_below) {
+      sk += g;  // spans of at least one tile: at most three contributors per cut tile
+    } else if (sk > 0 && sk * kb_total / g < kMinSpan) {
+      g = sk * kb_total / kMinSpan;
+      if (g > cap) g = cap;
     }
     if (sk > 0 && g >= 1 && sk * kb_total / g >= kMinSpan && sk * kb_total >= g) {
       const int64_t span_min = sk * kb_total / g;
@@ -204,20 +208,21 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
       pl.num_units = (int)tiles;
       pl.sk_tiles = (int)sk;
       pl.sk_slots = (int)((kb_total + span_min - 1) / span_min + 1);
-      pl.grid = (int)g;
+      pl.grid = (int)g * pl.cta_group;
     } else if (sk == 0) {
       pl.split_k = 1;  // whole waves only: plain data-parallel
       pl.num_units = (int)tiles;
-      pl.grid = (int)(tiles < cap ? tiles : cap);
+      pl.grid = (int)(tiles < cap ? tiles : cap) * pl.cta_group;
     }
   }
 
   const bool tickets = pl.split_k > 1 || pl.sk_tiles > 0;
-  if (tickets && tiles > (int64_t)(kCounterBytes / 4)) return B200_GEMM_ERR_TOO_LARGE;
-  // The ticket region has a fixed size so that it never overlaps an area another call used for partial sums.
-  pl.counter_bytes = tickets ? kCounterBytes : 0;
-  pl.partial_bytes = pl.sk_tiles > 0 ? (uint64_t)pl.sk_tiles * pl.sk_slots * kTileP * pl.tile_n * 4
-                     : pl.split_k > 1 ? (uint64_t)pl.num_units * kTileP * pl.tile_n * 4
+  if (tickets && tiles * pl.cta_group > (int64_t)(kCounterBytes / 4)) return B200_GEMM_ERR_TOO_LARGE;
+  // The ticket region has a fixed size and is reserved by every call that uses the workspace at all, so that no call
+  // ever writes partial sums or a repack image where another call keeps its tickets.
+  pl.counter_bytes = (tickets || pl.a_repacked || pl.b_repacked) ? kCounterBytes : 0;
+  pl.partial_bytes = pl.sk_tiles > 0 ? (uint64_t)pl.sk_tiles * pl.sk_slots * pl.tile_m * pl.tile_n * 4
+                     : pl.split_k > 1 ? (uint64_t)pl.num_units * pl.tile_m * pl.tile_n * 4
                                       : 0;
   const uint64_t ra = pl.a_repacked ? round_up((uint64_t)a_rows * r->ra_ld * 2, 256) : 0;
   const uint64_t rb = pl.b_repacked ? round_up((uint64_t)b_rows * r->rb_ld * 2, 256) : 0;
@@ -290,7 +295,7 @@ struct RepackJob {
 struct b200_gemm_handle {
   b200::GemmParams params;
   b200::KernelFn fn;
-  int grid, smem_bytes, device;
+  int grid, smem_bytes, device, cta_group;
   int n_repack;
   b200::RepackJob repack[2];
   b200_gemm_plan plan;
@@ -347,7 +352,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   const int64_t u_ld = pl.swap_ab ? ldb : lda, v_ld = pl.swap_ab ? lda : ldb;
   rc = encode_operand(&p.tmap_u, u_ptr, a->in_dtype, r.u_mn, r.P, a->k, u_ld, kTileP);
   if (rc) return rc;
-  rc = encode_operand(&p.tmap_v, v_ptr, a->in_dtype, r.v_mn, r.Q, a->k, v_ld, pl.tile_n);
+  rc = encode_operand(&p.tmap_v, v_ptr, a->in_dtype, r.v_mn, r.Q, a->k, v_ld, pl.tile_n / pl.cta_group);
   if (rc) return rc;
   p.out = a->out;
   p.bias = a->bias;
@@ -367,7 +372,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   p.out_dtype = a->out_dtype;
   p.in_dtype = a->in_dtype;
   p.u_mn_major = r.u_mn, p.v_mn_major = r.v_mn;
-  p.idesc = make_idesc(a->in_dtype, r.u_mn, r.v_mn, kTileP, pl.tile_n);
+  p.idesc = make_idesc(a->in_dtype, r.u_mn, r.v_mn, pl.tile_m, pl.tile_n);
   make_desc(r.u_mn, &p.u_desc_hi, &p.u_desc_lo, &p.u_kstep);
   make_desc(r.v_mn, &p.v_desc_hi, &p.v_desc_lo, &p.v_kstep);
 
@@ -376,6 +381,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   h->fn = var->fn[pl.stages];
   h->grid = pl.grid;
   h->smem_bytes = pl.smem_bytes;
+  h->cta_group = pl.cta_group;
   {
     std::lock_guard<std::mutex> lock(g_dev_mutex);
     if (!dev->attr_set[vi][pl.stages]) {
@@ -399,6 +405,15 @@ static int run(const b200_gemm_handle* h, cudaStream_t stream) {
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = h->smem_bytes;
   cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (h->cta_group == 2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
   cudaError_t e = cudaLaunchKernelEx(&cfg, h->fn, h->params);
   if (e != cudaSuccess) return set_cuda_error(e);
   return 0;

@@ -80,22 +80,24 @@ __device__ __forceinline__ void raster_tile(const GemmParams& p, int tile, int& 
   }
 }
 
-// Walks the work of CTA blockIdx.x; all three roles run the same walk.
+// Walks the work of one CTA (or CTA pair); all three roles run the same walk.
 //   split-K / data-parallel (sk_tiles == 0): units u = cta, cta+grid, ... ; unit = (tile, K slice).
 //   stream-K (sk_tiles > 0): first this CTA's equal share of the K blocks of tiles [0, sk_tiles) (a contiguous span
 //   that may cross tile boundaries), then whole tiles sk_tiles + cta, sk_tiles + cta + grid, ...
 struct WorkIter {
   long long sk_cur, sk_end, sk_total;
-  int next_u;
-  __device__ __forceinline__ void init(const GemmParams& p) {
+  int next_u, me, count;
+  // `me` of `count`: this CTA among the CTAs of the grid, or this CTA pair among the pairs.
+  __device__ __forceinline__ void init(const GemmParams& p, int me_, int count_) {
+    me = me_, count = count_;
     sk_total = (long long)p.sk_tiles * p.kb_total;
-    sk_cur = sk_total * blockIdx.x / gridDim.x;
-    sk_end = sk_total * (blockIdx.x + 1) / gridDim.x;
-    next_u = p.sk_tiles > 0 ? p.sk_tiles + (int)blockIdx.x : (int)blockIdx.x;
+    sk_cur = sk_total * me / count;
+    sk_end = sk_total * (me + 1) / count;
+    next_u = p.sk_tiles > 0 ? p.sk_tiles + me : me;
   }
-  // CTA that owns stream-K iteration x: the largest b with floor(b * total / grid) <= x.
+  // Walker that owns stream-K iteration x: the largest b with floor(b * total / count) <= x.
   __device__ __forceinline__ int owner(long long x) const {
-    return (int)(((x + 1) * gridDim.x + sk_total - 1) / sk_total) - 1;
+    return (int)(((x + 1) * count + sk_total - 1) / sk_total) - 1;
   }
   __device__ __forceinline__ bool next(const GemmParams& p, Unit& w) {
     if (sk_cur < sk_end) {
@@ -110,21 +112,21 @@ struct WorkIter {
         const int last = owner((long long)(w.tile + 1) * p.kb_total - 1);
         w.n_contrib = last - first + 1;
         w.slot0 = w.tile * p.sk_slots;
-        w.slot = w.slot0 + ((int)blockIdx.x - first);
+        w.slot = w.slot0 + (me - first);
       }
       return true;
     }
     if (p.sk_tiles > 0) {
       if (next_u >= p.num_tiles) return false;
       w.tile = next_u;
-      next_u += gridDim.x;
+      next_u += count;
       raster_tile(p, w.tile, w.tp, w.tq);
       w.kb0 = 0, w.kbn = p.kb_total, w.partial = 0;
       return true;
     }
     if (next_u >= p.num_units) return false;
     const int u = next_u;
-    next_u += gridDim.x;
+    next_u += count;
     w.tile = u / p.split_k;
     const int slice = u - w.tile * p.split_k;
     raster_tile(p, w.tile, w.tp, w.tq);
@@ -139,9 +141,12 @@ struct WorkIter {
   }
 };
 
-template <int TILE_Q, int STAGES>
+// CG = CTAs that share one output tile: 1, or 2 for a tcgen05 cta_group::2 pair (each CTA then holds 128 of the
+// tile's 256 U rows and half of its V rows).
+template <int TILE_Q, int STAGES, int CG>
 struct SmemLayout {
-  static constexpr int kVStageBytes = TILE_Q * kTileK * 2;
+  static constexpr int kVRows = TILE_Q / CG;
+  static constexpr int kVStageBytes = kVRows * kTileK * 2;
   static constexpr int kStageBytes = kUStageBytes + kVStageBytes;
   static constexpr int kRingBytes = STAGES * kStageBytes;
   static constexpr int kBiasOff = kRingBytes;            // float[256]
@@ -233,13 +238,15 @@ __device__ __forceinline__ float load_in_as_float(const void* ptr, long long i, 
   return __half2float(reinterpret_cast<const __half*>(ptr)[i]);
 }
 
-template <int TILE_Q, int STAGES>
+template <int TILE_Q, int STAGES, int CG>
 __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __grid_constant__ GemmParams p) {
-  using L = SmemLayout<TILE_Q, STAGES>;
+  using L = SmemLayout<TILE_Q, STAGES, CG>;
   constexpr int CW = TILE_Q >= 32 ? 32 : 16;  // columns per tcgen05.ld
   constexpr int NCHUNK = TILE_Q / CW;
   constexpr uint32_t kTmemCols = (2 * TILE_Q) < 32 ? 32 : 2 * TILE_Q;  // power of two for every TILE_Q in the menu
-  constexpr uint32_t kTxBytes = L::kStageBytes;
+  constexpr uint32_t kTxBytes = CG * L::kStageBytes;  // a pair's two CTAs both report to the leader's barrier
+  constexpr int kVRows = L::kVRows;
+  constexpr int kSlotVec = NCHUNK * (CW / 4) * kTileP;  // float4 per partial slot of one CTA
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -258,6 +265,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int rank = CG == 2 ? (int)cluster_ctarank() : 0;  // 0 = leader of the pair (issues the MMAs)
+  const int walker = CG == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int walkers = CG == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -266,7 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(accf_bar(b), 1);
-      mbar_init(acce_bar(b), kEpiThreads);
+      mbar_init(acce_bar(b), 4 * CG);  // one arrival per epilogue warp of every CTA of the pair
     }
     *abort_s = 0;
     *last_s = 0;
@@ -275,49 +285,61 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
     prefetch_tmap(&p.tmap_v);
   }
   if (warp == 1) {
-    tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_ptr_s)), kTmemCols);
-    tmem_relinquish<1>();
+    tmem_alloc<CG>(smem_u32(const_cast<uint32_t*>(tmem_ptr_s)), kTmemCols);
+    tmem_relinquish<CG>();
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) {  // the peer's barriers must exist before anything is signalled across the pair
+    cluster_arrive();
+    cluster_wait();
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_s;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer (one per CTA)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0;
       bool ok = true;
       WorkIter wi;
-      wi.init(p);
+      wi.init(p, walker, walkers);
       Unit w;
       while (ok && wi.next(p, w)) {
         const int u = w.tile;
-        const int p0 = w.tp * kTileP, q0 = w.tq * TILE_Q;
+        const int p0 = (w.tp * CG + rank) * kTileP, q0 = w.tq * TILE_Q + rank * kVRows;
         for (int kb = w.kb0; kb < w.kb0 + w.kbn; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_s)) {
+          if (!mbar_wait<CG == 2>(empty_bar(stage), phase ^ 1u, abort_s)) {
             report_abort(p, 0, u);
             ok = false;
             break;
           }
-          const uint32_t fb = full_bar(stage);
-          mbar_arrive_expect_tx(fb, kTxBytes);
+          // Data of both CTAs of a pair is counted on the leader's barrier, which the MMA thread waits on.
+          uint32_t fb = full_bar(stage);
+          if constexpr (CG == 2) fb = mapa_cluster(fb, 0);
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), kTxBytes);
           const uint32_t su = base + stage * L::kStageBytes;
           const uint32_t sv = su + kUStageBytes;
           const int k0 = kb * kTileK;
+          auto load = [&](uint32_t dst, const void* map, int x, int y) {
+            if constexpr (CG == 2)
+              tma_load_2d_pair(dst, map, x, y, fb);
+            else
+              tma_load_2d(dst, map, x, y, fb);
+          };
           if (!p.u_mn_major) {
-            tma_load_2d(su, &p.tmap_u, k0, p0, fb);
+            load(su, &p.tmap_u, k0, p0);
           } else {
-            tma_load_2d(su, &p.tmap_u, p0, k0, fb);
-            tma_load_2d(su + 8192u, &p.tmap_u, p0 + 64, k0, fb);
+            load(su, &p.tmap_u, p0, k0);
+            load(su + 8192u, &p.tmap_u, p0 + 64, k0);
           }
           if (!p.v_mn_major) {
-            tma_load_2d(sv, &p.tmap_v, k0, q0, fb);
+            load(sv, &p.tmap_v, k0, q0);
           } else {
 #pragma unroll
-            for (int j = 0; j < (TILE_Q >= 64 ? TILE_Q / 64 : 1); ++j) tma_load_2d(sv + 8192u * j, &p.tmap_v, q0 + 64 * j, k0, fb);
+            for (int j = 0; j < (kVRows >= 64 ? kVRows / 64 : 1); ++j) load(sv + 8192u * j, &p.tmap_v, q0 + 64 * j, k0);
           }
           ++issued;
           if (++stage == STAGES) {
@@ -326,7 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
           }
         }
       }
-      if (!ok) {
+      if (!ok && CG == 1) {
         // Loads already issued still write this CTA's smem: give each one a bounded chance to land.
         const int pending = issued < STAGES ? issued : STAGES;
         for (int i = 0; i < pending; ++i) {
@@ -340,30 +362,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
           while (!mbar_try_wait(full_bar(s), ph) && globaltimer_ns() - t0 < 100000000ull) {
           }
         }
+      } else if (!ok) {
+        // In a pair the byte counts live on the leader's barriers: wait a fixed, bounded time instead.
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 1000000ull) {
+        }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (the pair's leader only)
+    if (lane == 0 && rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
       WorkIter wi;
-      wi.init(p);
+      wi.init(p, walker, walkers);
       Unit w;
       for (; ok && wi.next(p, w); ++it) {
         const int u = w.tile;
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(acce_bar(buf), acc_phase ^ 1u, abort_s)) {
+        if (!mbar_wait<CG == 2>(acce_bar(buf), acc_phase ^ 1u, abort_s)) {
           report_abort(p, 1, u);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * TILE_Q;
         for (int kb = 0; kb < w.kbn; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_s)) {
+          if (!mbar_wait<CG == 2>(full_bar(stage), phase, abort_s)) {
             report_abort(p, 2, u);
             ok = false;
             break;
@@ -375,32 +402,45 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
           const uint64_t dv = (uint64_t(p.v_desc_hi) << 32) | uint64_t(p.v_desc_lo | ((sv >> 4) & 0x3fffu));
 #pragma unroll
           for (int j = 0; j < kTileK / kUmmaK; ++j) {
-            umma_f16<1>(d_tmem, du + uint64_t(j * p.u_kstep), dv + uint64_t(j * p.v_kstep), p.idesc,
-                        (kb | j) != 0 ? 1u : 0u);
+            umma_f16<CG>(d_tmem, du + uint64_t(j * p.u_kstep), dv + uint64_t(j * p.v_kstep), p.idesc,
+                         (kb | j) != 0 ? 1u : 0u);
           }
-          umma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          // Frees the stage, in every CTA of the pair, once these MMAs have read it.
+          if constexpr (CG == 2) {
+            umma_commit_pair(mapa_cluster(empty_bar(stage), 0));
+            umma_commit_pair(mapa_cluster(empty_bar(stage), 1));
+          } else {
+            umma_commit(empty_bar(stage));
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(accf_bar(buf));  // accumulator complete
+        if (ok) {  // accumulator complete: wake the epilogue of every CTA of the pair
+          if constexpr (CG == 2) {
+            umma_commit_pair(mapa_cluster(accf_bar(buf), 0));
+            umma_commit_pair(mapa_cluster(accf_bar(buf), 1));
+          } else {
+            umma_commit(accf_bar(buf));
+          }
+        }
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..5 of every CTA)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     const int row = quarter * 32 + lane;
     const int et = threadIdx.x - 64;  // 0..127
     int it = 0;
     WorkIter wi;
-    wi.init(p);
+    wi.init(p, walker, walkers);
     Unit w;
     for (; wi.next(p, w); ++it) {
       const int u = w.tile;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int prow = w.tp * kTileP + row;
+      const int prow = (w.tp * CG + rank) * kTileP + row;
       const int qbase = w.tq * TILE_Q;
       const bool direct = !w.partial;
 
@@ -419,14 +459,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         }
       }
 
-      if (!mbar_wait<false, false>(accf_bar(buf), acc_phase, abort_s)) {
+      if (!mbar_wait<CG == 2, false>(accf_bar(buf), acc_phase, abort_s)) {
         report_abort(p, 3, u);
         break;
       }
       tc_fence_after();
       const uint32_t t_acc = tmem_base + buf * TILE_Q + (uint32_t(quarter * 32) << 16);
-      float* part = nullptr;
-      if (!direct) part = p.partials + ((size_t)w.slot * NCHUNK) * (kTileP * CW) + (size_t)row * CW;
+      float4* part = nullptr;
+      if (!direct) part = reinterpret_cast<float4*>(p.partials) + (size_t)(w.slot * CG + rank) * kSlotVec + row;
 
 #pragma unroll 1
       for (int c = 0; c < NCHUNK; ++c) {
@@ -437,9 +477,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
           tmem_ld_32x16(t_acc + c * CW, r);
         tmem_ld_wait();
         if (c == NCHUNK - 1) {
-          // Everything this thread needs is in registers: hand the accumulator back to the MMA warp.
+          // Everything this warp needs is in registers: hand the accumulator back to the MMA thread.
           tc_fence_before();
-          mbar_arrive(acce_bar(buf));
+          __syncwarp();
+          if (lane == 0) {
+            if (CG == 2 && rank != 0)
+              mbar_arrive_cluster(acce_bar(buf), 0);
+            else
+              mbar_arrive(acce_bar(buf));
+          }
         }
         float v[CW];
 #pragma unroll
@@ -447,41 +493,58 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         if (direct) {
           finalize_chunk<CW>(p, v, prow, qbase + c * CW, bias_s + c * CW, bias_p);
         } else {
-          float4* dst = reinterpret_cast<float4*>(part + (size_t)c * (kTileP * CW));
+          // slot layout [chunk][4-column group][row][4]: one warp store covers 512 contiguous bytes
+          float4* dst = part + (size_t)c * (CW / 4) * kTileP;
 #pragma unroll
-          for (int i = 0; i < CW; i += 4) __stcg(dst + i / 4, make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]));
+          for (int j = 0; j < CW / 4; ++j)
+            __stcg(dst + j * kTileP, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
         }
       }
 
       if (!direct) {
-        // Ticket: the CTA that arrives last at this tile sums all slices in slice order.
+        // Ticket: the CTA that arrives last at this (half-)tile sums all contributions in slot order.
         __threadfence();
         named_bar_sync(2, kEpiThreads);
         if (et == 0) {
-          const int t = atomicAdd(p.tickets + w.tile, 1);
+          int* ticket = p.tickets + (w.tile * CG + rank);
+          const int t = atomicAdd(ticket, 1);
           const int last = (t == w.n_contrib - 1) ? 1 : 0;
-          if (last) p.tickets[w.tile] = 0;  // self-cleaning: nobody else touches it until the next launch
+          if (last) *ticket = 0;  // self-cleaning: nobody else touches it until the next launch
           *last_s = last;
         }
         named_bar_sync(2, kEpiThreads);
         const int last = *last_s;
         if (last) {
           __threadfence();
-          const float* tp0 = p.partials + ((size_t)w.slot0 * NCHUNK) * (kTileP * CW) + (size_t)row * CW;
+          const float4* tp0 = reinterpret_cast<const float4*>(p.partials) + (size_t)(w.slot0 * CG + rank) * kSlotVec + row;
+          constexpr int kBatch = 4;  // contributors whose loads are in flight together
 #pragma unroll 1
           for (int c = 0; c < NCHUNK; ++c) {
             float v[CW];
 #pragma unroll
             for (int i = 0; i < CW; ++i) v[i] = 0.f;
-            for (int s = 0; s < w.n_contrib; ++s) {
-              const float4* src = reinterpret_cast<const float4*>(tp0 + ((size_t)s * NCHUNK + c) * (kTileP * CW));
+#pragma unroll 1
+            for (int s0 = 0; s0 < w.n_contrib; s0 += kBatch) {
+              float4 x[kBatch][CW / 4];
 #pragma unroll
-              for (int i = 0; i < CW; i += 4) {
-                const float4 x = __ldcg(src + i / 4);
-                v[i] += x.x;
-                v[i + 1] += x.y;
-                v[i + 2] += x.z;
-                v[i + 3] += x.w;
+              for (int bb = 0; bb < kBatch; ++bb) {
+                if (s0 + bb < w.n_contrib) {
+                  const float4* src = tp0 + (size_t)(s0 + bb) * (CG * kSlotVec) + (size_t)c * ((CW / 4) * kTileP);
+#pragma unroll
+                  for (int jj = 0; jj < CW / 4; ++jj) x[bb][jj] = __ldcg(src + jj * kTileP);
+                }
+              }
+#pragma unroll
+              for (int bb = 0; bb < kBatch; ++bb) {
+                if (s0 + bb < w.n_contrib) {
+#pragma unroll
+                  for (int jj = 0; jj < CW / 4; ++jj) {
+                    v[4 * jj] += x[bb][jj].x;
+                    v[4 * jj + 1] += x[bb][jj].y;
+                    v[4 * jj + 2] += x[bb][jj].z;
+                    v[4 * jj + 3] += x[bb][jj].w;
+                  }
+                }
               }
             }
             finalize_chunk<CW>(p, v, prow, qbase + c * CW, bias_s + c * CW, bias_p);
@@ -495,10 +558,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) {  // no CTA of a pair leaves while its peer may still signal it or use its TMEM half
+    cluster_arrive();
+    cluster_wait();
+  }
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc<1>(tmem_base, kTmemCols);
+    tmem_dealloc<CG>(tmem_base, kTmemCols);
   }
 }
 

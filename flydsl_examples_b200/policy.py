@@ -17,7 +17,8 @@ from typing import Optional
 TILE_M = 128  # rows per CTA on the MMA M axis (TMEM lanes)
 TILE_K = 64   # one 128-byte swizzle span of 16-bit data
 TILE_N_MENU = (16, 32, 64, 128, 256)
-MAX_STAGES = {16: 10, 32: 10, 64: 8, 128: 6, 256: 4}
+MAX_STAGES = {16: 10, 32: 10, 64: 8, 128: 6, 256: 4}          # one CTA per tile
+MAX_STAGES_PAIR = {128: 8, 256: 6}                            # a CTA pair per 256-row tile (cta_group 2)
 SMEM_LIMIT = 232448
 TMEM_COLUMNS = 512
 NUM_SMS_DEFAULT = 148
@@ -49,9 +50,10 @@ class Policy:
         return asdict(self)
 
 
-def smem_bytes(tile_n: int, stages: int) -> int:
-    """Dynamic shared memory of one CTA: the ring, the bias slice, the barriers and alignment slack."""
-    return stages * (TILE_M * TILE_K * 2 + tile_n * TILE_K * 2) + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024
+def smem_bytes(tile_n: int, stages: int, cta_group: int = 1) -> int:
+    """Dynamic shared memory of one CTA: the ring, the bias slice, the barriers and alignment slack. In a pair
+    each CTA holds 128 of the tile's 256 rows and half of its tile_n columns."""
+    return stages * (TILE_M * TILE_K * 2 + (tile_n // cta_group) * TILE_K * 2) + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024
 
 
 def split_k_slices(k: int, split_k: int) -> list[tuple[int, int]]:
@@ -81,15 +83,15 @@ def raster(tile: int, tiles_p: int, tiles_q: int, group: int) -> tuple[int, int]
 def stream_k_plan(tiles: int, kb_total: int, cap: int, min_span: int = 4) -> tuple[int, int, int]:
     """(grid, sk_tiles, sk_slots) of the stream-K schedule; sk_tiles == 0 means plain data-parallel.
     The tiles that do not fill a whole wave of `cap` CTAs are cut into equal contiguous spans of K blocks, one
-    span per CTA; if a span would be shorter than `min_span` blocks one full wave is added to the cut region, or,
-    with less than one wave of tiles, fewer CTAs are used. Mirrors the planner in csrc/gemm_api.cu."""
+    span per CTA; a remainder whose spans would be shorter than half a tile borrows one full wave (so a cut tile
+    has at most three contributors); with less than one wave of tiles, spans shorter than `min_span` blocks make
+    the grid shrink instead. Mirrors the planner in csrc/gemm_api.cu."""
     g = cap
     sk = tiles % g if tiles >= g else tiles
-    if sk > 0 and sk * kb_total // g < min_span:
-        if tiles > g:
-            sk += g
-        else:
-            g = min(cap, sk * kb_total // min_span)
+    if sk > 0 and tiles > g and sk * kb_total // g < max(min_span, kb_total // 2):
+        sk += g
+    elif sk > 0 and sk * kb_total // g < min_span:
+        g = min(cap, sk * kb_total // min_span)
     if sk > 0 and g >= 1 and sk * kb_total // g >= min_span:
         span_min = sk * kb_total // g
         return g, sk, (kb_total + span_min - 1) // span_min + 1
@@ -127,11 +129,14 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
     """Return None when the policy is runnable for this problem, else the reason."""
     if pol.tile_n not in TILE_N_MENU:
         return f"tile_n must be one of {TILE_N_MENU}, got {pol.tile_n}"
-    if pol.cta_group not in (1,):
-        return f"cta_group must be 1, got {pol.cta_group}"
-    if pol.stages < 0 or pol.stages == 1 or pol.stages > MAX_STAGES[pol.tile_n]:
-        return f"stages must be 0 (auto) or 2..{MAX_STAGES[pol.tile_n]} for tile_n={pol.tile_n}, got {pol.stages}"
-    if pol.stages and smem_bytes(pol.tile_n, pol.stages) > SMEM_LIMIT:
+    if pol.cta_group not in (1, 2):
+        return f"cta_group must be 1 or 2, got {pol.cta_group}"
+    stage_menu = MAX_STAGES if pol.cta_group == 1 else MAX_STAGES_PAIR
+    if pol.tile_n not in stage_menu:
+        return f"cta_group 2 needs tile_n in {tuple(MAX_STAGES_PAIR)}, got {pol.tile_n}"
+    if pol.stages < 0 or pol.stages == 1 or pol.stages > stage_menu[pol.tile_n]:
+        return f"stages must be 0 (auto) or 2..{stage_menu[pol.tile_n]} for tile_n={pol.tile_n}, got {pol.stages}"
+    if pol.stages and smem_bytes(pol.tile_n, pol.stages, pol.cta_group) > SMEM_LIMIT:
         return "shared memory ring exceeds 227 KB"
     if pol.split_k < 1:
         return f"split_k must be >= 1, got {pol.split_k}"
@@ -143,8 +148,8 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
     a_mn = layout[0] == "t"
     b_mn = layout[1] == "n"
     v_mn = a_mn if pol.swap_ab else b_mn
-    if v_mn and pol.tile_n < 64:
-        return "tile_n < 64 needs the tile_n-side operand to be K-contiguous"
+    if v_mn and pol.tile_n // pol.cta_group < 64:
+        return "fewer than 64 tile_n columns per CTA needs the tile_n-side operand to be K-contiguous"
     if 2 * pol.tile_n > TMEM_COLUMNS:
         return "two accumulators do not fit in 512 TMEM columns"
     return None
