@@ -52,6 +52,8 @@ class Args(C.Structure):
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_uint64),
         ("status", C.c_void_p),
+        ("trace", C.c_void_p),
+        ("trace_words", C.c_uint64),
     ]
 
 

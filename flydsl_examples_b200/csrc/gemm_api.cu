@@ -347,6 +347,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
 
   GemmParams& p = h->params;
   memset(&p, 0, sizeof(p));
+  const b200_gemm_policy& pol = a->policy;
   const void* u_ptr = pl.swap_ab ? pb : pa;
   const void* v_ptr = pl.swap_ab ? pa : pb;
   const int64_t u_ld = pl.swap_ab ? ldb : lda, v_ld = pl.swap_ab ? lda : ldb;
@@ -359,6 +360,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   p.tickets = reinterpret_cast<int*>(ws);
   p.partials = reinterpret_cast<float*>(ws + r.off_partials);
   p.status = a->status;
+  p.trace = (a->trace != nullptr && a->trace_words >= (uint64_t)pl.grid * kTraceRoles * kTraceItems * kTraceStamps) ? reinterpret_cast<unsigned long long*>(a->trace) : nullptr;
   p.ldo = a->ldo;
   p.P = r.P, p.Q = r.Q, p.K = (int)a->k;
   p.tiles_p = pl.tiles_p, p.tiles_q = pl.tiles_q, p.num_tiles = pl.tiles_p * pl.tiles_q;

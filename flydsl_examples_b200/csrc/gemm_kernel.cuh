@@ -38,6 +38,7 @@ struct alignas(64) GemmParams {
   float* partials;  // [tile][slice][chunk][128][CW] fp32
   int* tickets;     // [tile]
   int* status;      // int32[4] or null
+  unsigned long long* trace;  // optional timeline: [cta][role 0..3][item 0..15][4] stamps / counters, or null
   long long ldo;    // output row stride (elements)
   int P, Q, K;
   int tiles_p, tiles_q, num_tiles;
@@ -155,6 +156,17 @@ struct SmemLayout {
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynBytes = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
+
+constexpr int kTraceRoles = 4, kTraceItems = 16, kTraceStamps = 4;
+__device__ __forceinline__ void trace_stamp(const GemmParams& p, int role, int item, int k) {
+  if (p.trace != nullptr && item < kTraceItems)
+    p.trace[(((size_t)blockIdx.x * kTraceRoles + role) * kTraceItems + item) * kTraceStamps + k] = globaltimer_ns();
+}
+
+__device__ __forceinline__ void trace_value(const GemmParams& p, int role, int item, int k, long long v) {
+  if (p.trace != nullptr && item < kTraceItems)
+    p.trace[(((size_t)blockIdx.x * kTraceRoles + role) * kTraceItems + item) * kTraceStamps + k] = (unsigned long long)v;
+}
 
 __device__ __forceinline__ void report_abort(const GemmParams& p, int role, int unit) {
   if (p.status != nullptr) {
@@ -307,15 +319,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       WorkIter wi;
       wi.init(p, walker, walkers);
       Unit w;
-      while (ok && wi.next(p, w)) {
+      int item = 0;
+      for (; ok && wi.next(p, w); ++item) {
         const int u = w.tile;
         const int p0 = (w.tp * CG + rank) * kTileP, q0 = w.tq * TILE_Q + rank * kVRows;
+        trace_stamp(p, 0, item, 0);
+        int stalls = 0;
         for (int kb = w.kb0; kb < w.kb0 + w.kbn; ++kb) {
+          if (p.trace != nullptr && !mbar_try_wait(empty_bar(stage), phase ^ 1u)) ++stalls;
           if (!mbar_wait<CG == 2>(empty_bar(stage), phase ^ 1u, abort_s)) {
             report_abort(p, 0, u);
             ok = false;
             break;
           }
+          if (kb == w.kb0) trace_stamp(p, 0, item, 1);
           // Data of both CTAs of a pair is counted on the leader's barrier, which the MMA thread waits on.
           uint32_t fb = full_bar(stage);
           if constexpr (CG == 2) fb = mapa_cluster(fb, 0);
@@ -347,6 +364,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
             phase ^= 1u;
           }
         }
+        trace_stamp(p, 0, item, 2);
+        trace_value(p, 0, item, 3, stalls);
       }
       if (!ok && CG == 1) {
         // Loads already issued still write this CTA's smem: give each one a bounded chance to land.
@@ -371,7 +390,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (the pair's leader only)
-    if (lane == 0 && rank == 0) {
+    // The whole warp walks the loop so that control flow and operands stay warp-uniform; lane 0 polls the
+    // barriers and the verdict is broadcast, one elected lane issues the tensor-core instructions.
+    if (rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -379,52 +400,84 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       WorkIter wi;
       wi.init(p, walker, walkers);
       Unit w;
+      const bool tracing = p.trace != nullptr;
       for (; ok && wi.next(p, w); ++it) {
         const int u = w.tile;
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait<CG == 2>(acce_bar(buf), acc_phase ^ 1u, abort_s)) {
-          report_abort(p, 1, u);
+        int good = 1;
+        if (lane == 0) good = mbar_wait<CG == 2>(acce_bar(buf), acc_phase ^ 1u, abort_s) ? 1 : 0;
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) {
+          if (lane == 0) report_abort(p, 1, u);
           break;
         }
         tc_fence_after();
+        if (lane == 0) trace_stamp(p, 1, it, 0);
+        int stalls = 0;
+        long long c_wait = 0, c_mma = 0, c_commit = 0;
         const uint32_t d_tmem = tmem_base + buf * TILE_Q;
         for (int kb = 0; kb < w.kbn; ++kb) {
-          if (!mbar_wait<CG == 2>(full_bar(stage), phase, abort_s)) {
-            report_abort(p, 2, u);
+          long long c0 = 0, c1 = 0, c3 = 0;
+          if (tracing) c0 = clock64();
+          if (lane == 0) {
+            if (tracing && !mbar_try_wait(full_bar(stage), phase)) ++stalls;
+            good = mbar_wait<CG == 2>(full_bar(stage), phase, abort_s) ? 1 : 0;
+          }
+          good = __shfl_sync(0xffffffffu, good, 0);
+          if (!good) {
+            if (lane == 0) report_abort(p, 2, u);
             ok = false;
             break;
           }
           tc_fence_after();
+          if (tracing) c1 = clock64();
+          if (kb == 0 && lane == 0) trace_stamp(p, 1, it, 1);
           const uint32_t su = base + stage * L::kStageBytes;
           const uint32_t sv = su + kUStageBytes;
           const uint64_t du = (uint64_t(p.u_desc_hi) << 32) | uint64_t(p.u_desc_lo | ((su >> 4) & 0x3fffu));
           const uint64_t dv = (uint64_t(p.v_desc_hi) << 32) | uint64_t(p.v_desc_lo | ((sv >> 4) & 0x3fffu));
+          if (elect_one()) {
 #pragma unroll
-          for (int j = 0; j < kTileK / kUmmaK; ++j) {
-            umma_f16<CG>(d_tmem, du + uint64_t(j * p.u_kstep), dv + uint64_t(j * p.v_kstep), p.idesc,
-                         (kb | j) != 0 ? 1u : 0u);
+            for (int j = 0; j < kTileK / kUmmaK; ++j) {
+              umma_f16<CG>(d_tmem, du + uint64_t(j * p.u_kstep), dv + uint64_t(j * p.v_kstep), p.idesc,
+                           (kb | j) != 0 ? 1u : 0u);
+            }
+            if (tracing) c3 = clock64();
+            // Frees the stage, in every CTA of the pair, once these MMAs have read it.
+            if constexpr (CG == 2) {
+              umma_commit_pair(mapa_cluster(empty_bar(stage), 0));
+              umma_commit_pair(mapa_cluster(empty_bar(stage), 1));
+            } else {
+              umma_commit(empty_bar(stage));
+            }
+            if (tracing) {
+              const long long c4 = clock64();
+              c_wait += c1 - c0, c_mma += c3 - c1, c_commit += c4 - c3;
+            }
           }
-          // Frees the stage, in every CTA of the pair, once these MMAs have read it.
-          if constexpr (CG == 2) {
-            umma_commit_pair(mapa_cluster(empty_bar(stage), 0));
-            umma_commit_pair(mapa_cluster(empty_bar(stage), 1));
-          } else {
-            umma_commit(empty_bar(stage));
-          }
+          __syncwarp();
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) {  // accumulator complete: wake the epilogue of every CTA of the pair
-          if constexpr (CG == 2) {
-            umma_commit_pair(mapa_cluster(accf_bar(buf), 0));
-            umma_commit_pair(mapa_cluster(accf_bar(buf), 1));
-          } else {
-            umma_commit(accf_bar(buf));
+        if (elect_one()) {
+          trace_stamp(p, 1, it, 2);
+          trace_value(p, 1, it, 3, stalls);
+          trace_value(p, 3, it, 0, c_wait);
+          trace_value(p, 3, it, 2, c_mma);
+          trace_value(p, 3, it, 3, c_commit);
+          if (ok) {  // accumulator complete: wake the epilogue of every CTA of the pair
+            if constexpr (CG == 2) {
+              umma_commit_pair(mapa_cluster(accf_bar(buf), 0));
+              umma_commit_pair(mapa_cluster(accf_bar(buf), 1));
+            } else {
+              umma_commit(accf_bar(buf));
+            }
           }
         }
+        __syncwarp();
       }
     }
   } else {
@@ -464,6 +517,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         break;
       }
       tc_fence_after();
+      if (et == 0) {
+        trace_stamp(p, 2, it, 0);
+        trace_value(p, 2, it, 3, clock64());
+      }
       const uint32_t t_acc = tmem_base + buf * TILE_Q + (uint32_t(quarter * 32) << 16);
       float4* part = nullptr;
       if (!direct) part = reinterpret_cast<float4*>(p.partials) + (size_t)(w.slot * CG + rank) * kSlotVec + row;
@@ -501,6 +558,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         }
       }
 
+      if (et == 0) trace_stamp(p, 2, it, 1);
       if (!direct) {
         // Ticket: the CTA that arrives last at this (half-)tile sums all contributions in slot order.
         __threadfence();
@@ -552,6 +610,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         }
         named_bar_sync(2, kEpiThreads);  // last_s may be rewritten by the next unit
       }
+      if (et == 0) trace_stamp(p, 2, it, 2);
     }
   }
 

@@ -169,6 +169,17 @@ def make_gemm_a16w16_param_and_validate(m: int, n: int, k: int, kwargs: dict):
     return pol if _policy.validate(pol, m, n, k, layout) is None else None
 
 
+_trace_buffer: Optional[torch.Tensor] = None
+
+
+def set_trace_buffer(buf: Optional[torch.Tensor]) -> None:
+    """Profiling aid: while set (a CUDA int64 tensor of at least grid*256 elements), every newly prepared call
+    records per-CTA role timelines into it (see `trace` in include/b200_gemm.h). Pass None to turn it off."""
+    global _trace_buffer
+    _trace_buffer = buf
+    clear_prepared_calls()
+
+
 def _fill_args(a, b, out, bias, pol: _policy.Policy, a_t: bool, b_t: bool) -> _lib.Args:
     m, k = a.shape
     n = b.shape[1]
@@ -361,6 +372,9 @@ def gemm_a16w16(
             args.workspace = ws.buf.data_ptr()
             args.workspace_bytes = ws.buf.numel()
         args.status = ws.status.data_ptr()
+        if _trace_buffer is not None:
+            args.trace = _trace_buffer.data_ptr()
+            args.trace_words = _trace_buffer.numel()
         handle = C.c_void_p()
         rc = lib.b200_gemm_prepare(C.byref(args), C.byref(handle))
         if rc != 0:

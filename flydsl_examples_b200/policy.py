@@ -155,42 +155,56 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
     return None
 
 
+# Rough cost of one 64-deep K block of a tile, in SM cycles, used only to rank candidate tilings. The tensor pipe
+# needs 128 cycles per 128 x 256 x 16 MMA; one thread issues them and pays a fixed price per K block (barrier poll,
+# four MMAs, commit), which is what bounds narrow tiles; the fed fraction comes from ncu on large GEMMs
+# (0.72 with one CTA per tile, 0.87 with a CTA pair).
+_KBLOCK_CYCLES = {(1, 256): 512 / 0.72, (2, 256): 512 / 0.87, (1, 128): 340.0, (1, 64): 300.0, (1, 32): 310.0, (1, 16): 320.0}
+_FIXED_CYCLES = 6000.0  # launch tail, pipeline fill, last epilogue
+
+
+def _auto_split(tiles: int, kb: int, walkers: int) -> int:
+    """K slices per tile when the tiles alone cannot occupy the machine."""
+    if tiles * 2 <= walkers and kb >= 8:
+        return max(1, min(walkers // tiles, kb // 4, 64))
+    return 1
+
+
+def _estimate_cycles(p_ext: int, q: int, kb: int, cta_group: int, tile_n: int, num_sms: int) -> float:
+    walkers = max(1, num_sms // cta_group)
+    tiles = -(-p_ext // (TILE_M * cta_group)) * -(-q // tile_n)
+    split = _auto_split(tiles, kb, walkers)
+    waves = -(-(tiles * split) // walkers)
+    epilogue = 1000.0 + 500.0 * tile_n / 256
+    fixup = (1500.0 + 400.0 * split) if split > 1 else 0.0
+    return _FIXED_CYCLES + waves * (-(-kb // split) * _KBLOCK_CYCLES[(cta_group, tile_n)] + epilogue) + fixup
+
+
 def heuristic(m: int, n: int, k: int, layout: str = "nt", num_sms: int = NUM_SMS_DEFAULT) -> Policy:
-    """Shape-driven default used when the caller passes no Blackwell keys."""
+    """Shape-driven default used when the caller passes no Blackwell keys and the tuned table has no entry."""
     a_mn = layout[0] == "t"
     b_mn = layout[1] == "n"
     kb = max(1, (k + TILE_K - 1) // TILE_K)
     swap = m <= 64 and n > m
     if swap:
-        q, v_mn = m, a_mn
-        p_ext = n
+        q, v_mn, p_ext = m, a_mn, n
     else:
-        q, v_mn = n, b_mn
-        p_ext = m
+        q, v_mn, p_ext = n, b_mn, m
     menu = [t for t in TILE_N_MENU if not (v_mn and t < 64)]
-    tiles_p = (p_ext + TILE_M - 1) // TILE_M
+    cta_group = 1
     if swap:
         tile_n = next((t for t in menu if t >= q), menu[-1])
     else:
-        # Larger N tiles reuse each U stage more; smaller ones quantise better on few tiles.
-        eff = {256: 1.0, 128: 0.9, 64: 0.65, 32: 0.4, 16: 0.25}
-        best, best_score = menu[-1], -1.0
-        for t in menu:
-            if t > max(64, 1 << (max(q, 1) - 1).bit_length()):
-                continue
-            tiles = tiles_p * ((q + t - 1) // t)
-            waves = math.ceil(tiles / num_sms)
-            used = (q / (((q + t - 1) // t) * t))
-            score = eff[t] * used * tiles / (waves * num_sms)
-            if score > best_score + 1e-9:
-                best, best_score = t, score
-        tile_n = best
-    tiles = tiles_p * ((q + tile_n - 1) // tile_n)
-    split = 1
-    if tiles * 2 <= num_sms and kb >= 8:
-        split = max(1, min(num_sms // tiles, kb // 4, 64))
-    group = 8 if (tiles >= 2 * num_sms and not swap) else 0
-    return Policy(tile_n=tile_n, split_k=split, group_m=group, swap_ab=swap)
+        cands = [(1, t) for t in menu if t <= max(64, 1 << (max(q, 1) - 1).bit_length())]
+        if p_ext > TILE_M and q > 128:
+            cands.append((2, 256))
+        best = min(cands, key=lambda c: (_estimate_cycles(p_ext, q, kb, c[0], c[1], num_sms), -c[1], -c[0]))
+        cta_group, tile_n = best
+    walkers = num_sms // cta_group
+    tiles = -(-p_ext // (TILE_M * cta_group)) * -(-q // tile_n)
+    split = _auto_split(tiles, kb, walkers)
+    group = 8 if (tiles >= 2 * walkers and not swap) else 0
+    return Policy(tile_n=tile_n, split_k=split, group_m=group, swap_ab=swap, cta_group=cta_group)
 
 
 def from_user_kwargs(user_kwargs: dict, m: int, n: int, k: int, layout: str, num_sms: int = NUM_SMS_DEFAULT) -> Policy:
@@ -205,7 +219,7 @@ def from_user_kwargs(user_kwargs: dict, m: int, n: int, k: int, layout: str, num
     if native:
         # A Blackwell policy is taken literally: nothing the caller left out is second-guessed by the heuristic
         # except the tile, which falls back to the heuristic's choice.
-        fields.update(split_k=1, group_m=0, swap_ab=False, stages=0)
+        fields.update(split_k=1, group_m=0, swap_ab=False, stages=0, cta_group=1)
         for key in BLACKWELL_KEYS + ("stages", "split_k", "group_m"):
             if key in user_kwargs:
                 fields[key] = user_kwargs[key]

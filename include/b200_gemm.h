@@ -77,6 +77,12 @@ typedef struct b200_gemm_args {
   uint64_t workspace_bytes;
   int32_t* status; /* device int32[4], or NULL. Written only when a bounded wait inside a kernel gave up:
                       [0]=error code (1), [1]=CTA, [2]=role, [3]=unit                                         */
+  uint64_t* trace; /* device uint64[trace_words], or NULL. Profiling aid: every CTA records %globaltimer stamps of its
+                      producer / MMA / epilogue roles for its first 16 work items: [cta][role 0..3][item][4] (begin, first
+                      data / accumulator handed back, end, and a counter: stalled waits, or clock64 for the epilogue;
+                      role 3 = cycles the MMA thread spent in wait / fence / issue / commit). Needs
+                      grid * 4 * 16 * 4 words; ignored when smaller                                            */
+  uint64_t trace_words;
 } b200_gemm_args;
 
 /* What a call would do, for tests, the tuner and workspace sizing. */

@@ -158,6 +158,37 @@ def test_split_k_shapes(layout, dtype, idx):
                  repeats=2, prefill="randn")
 
 
+PAIR = [  # a CTA pair per 256-row tile (tcgen05 cta_group::2)
+    (256, 256, 64, {"tile_n": 256, "cta_group": 2}),
+    (1024, 1024, 512, {"tile_n": 256, "cta_group": 2}),
+    (512, 384, 512, {"tile_n": 128, "cta_group": 2}),
+    (700, 900, 520, {"tile_n": 256, "cta_group": 2}),              # ragged: second CTA of a pair partly / fully out of range
+    (130, 300, 1000, {"tile_n": 128, "cta_group": 2}),
+    (512, 512, 4096, {"tile_n": 256, "cta_group": 2, "split_k": 4}),
+    (1000, 3000, 4100, {"tile_n": 256, "cta_group": 2, "stream_k": True}),
+    (4096, 4096, 1024, {"tile_n": 256, "cta_group": 2, "group_m": 4}),
+    (2048, 4096, 4096, {"tile_n": 256, "cta_group": 2, "stream_k": True, "group_m": 8}),
+]
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("idx", range(len(PAIR)))
+def test_cta_pair_shapes(dtype, idx):
+    m, n, k, kw = PAIR[idx]
+    for layout in (LAYOUTS if m * n * k <= 1 << 32 else ("nt", "tn")):
+        for out_dtype in (None, "fp32"):
+            run_case(O.Case("pair", dtype, layout, m, n, k, seed=400 + idx, bias_std=0.5, out_dtype=out_dtype, user_kwargs=kw),
+                     repeats=2, prefill="randn")
+
+
+def test_default_policy_picks_a_pair_for_large_shapes():
+    a = torch.empty(8192, 4096, dtype=torch.bfloat16, device=DEV)
+    b = torch.empty(4096, 4096, dtype=torch.bfloat16, device=DEV).t()
+    pl = plan(a, b, "nt", {})
+    assert pl["cta_group"] == 2 and pl["tile_m"] == 256 and pl["tile_n"] == 256
+    run_case(O.Case("pair_default", "bf16", "nt", 4096, 4096, 2048, seed=9, bias_std=0.5))
+
+
 STREAM_K = [  # shapes whose tile count is not a multiple of the SM count, or smaller than it
     (2048, 4096, 4096, {"tile_n": 256, "stream_k": True}),                 # 256 tiles: 108 cut into spans
     (1000, 3000, 4100, {"tile_n": 256, "stream_k": True}),                 # 96 tiles: all cut
