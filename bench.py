@@ -36,7 +36,7 @@ import torch  # noqa: E402
 L2_BYTES_NOMINAL = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
 # under profiles/ (None until captured for that workload).
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {"c2": 53.5e6}  # profiles/gemm_sm100_kernel_config2.md
 
 
 def measured_peaks() -> dict:
