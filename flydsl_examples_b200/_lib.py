@@ -13,6 +13,7 @@ from pathlib import Path
 from . import build as _build
 
 DTYPE_FP32, DTYPE_BF16, DTYPE_FP16 = 1, 2, 3
+STATIC_SCRATCH_BYTES = 16 << 20  # B200_GEMM_STATIC_SCRATCH_BYTES
 
 ERR_TEXT_FALLBACK = "b200_gemm error"
 
@@ -90,6 +91,7 @@ class Plan(C.Structure):
 
 EXPORTS = (
     "b200_gemm_a16w16",
+    "b200_gemm_a16w16_static_scratch",
     "b200_gemm_prepare",
     "b200_gemm_launch",
     "b200_gemm_release",
@@ -129,6 +131,8 @@ def load() -> C.CDLL:
     lib = C.CDLL(str(path))
     lib.b200_gemm_a16w16.argtypes = [C.POINTER(Args), C.c_void_p]
     lib.b200_gemm_a16w16.restype = C.c_int
+    lib.b200_gemm_a16w16_static_scratch.argtypes = [C.POINTER(Args), C.c_void_p]
+    lib.b200_gemm_a16w16_static_scratch.restype = C.c_int
     lib.b200_gemm_prepare.argtypes = [C.POINTER(Args), C.POINTER(C.c_void_p)]
     lib.b200_gemm_prepare.restype = C.c_int
     lib.b200_gemm_launch.argtypes = [C.c_void_p, C.c_void_p]

@@ -421,9 +421,61 @@ static int run(const b200_gemm_handle* h, cudaStream_t stream) {
   return 0;
 }
 
+// ------------------------------------------------------------------ built-in scratch for callers that cannot allocate
+// Lives in every GPU that loads this library, for the life of the process. In host code the name below is only a
+// stand-in for the device symbol; its device address is looked up once per device with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_static_scratch[B200_GEMM_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_ptr[kMaxDevices] = {};
+static std::mutex g_static_scratch_mutex;
+
+static int static_scratch_for_current_device(void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_GEMM_ERR_LAUNCH;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+    if (e != cudaSuccess) return set_cuda_error(e);
+    if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 255) != 0) return B200_GEMM_ERR_WORKSPACE;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return 0;
+}
+
 }  // namespace b200
 
 extern "C" {
+
+int b200_gemm_a16w16_static_scratch(const b200_gemm_args* args, void* cuda_stream) {
+  if (args == nullptr) return B200_GEMM_ERR_BAD_ARG;
+  b200_gemm_plan plan;
+  int rc = b200_gemm_plan_query(args, &plan);
+  if (rc) return rc;
+  if (plan.workspace_bytes > (uint64_t)B200_GEMM_STATIC_SCRATCH_BYTES) return B200_GEMM_ERR_TOO_LARGE;
+  b200_gemm_args local = *args;
+  local.workspace = nullptr;
+  local.workspace_bytes = 0;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+  if (plan.workspace_bytes > 0) {
+    void* scratch = nullptr;
+    rc = b200::static_scratch_for_current_device(&scratch);
+    if (rc) return rc;
+    local.workspace = scratch;
+    local.workspace_bytes = B200_GEMM_STATIC_SCRATCH_BYTES;
+    // The array keeps whatever the previous call left. Partial sums and repack images are fully rewritten before
+    // they are read; the tickets must start at zero, so the ones this call uses are cleared first (same stream).
+    if (plan.split_k > 1 || plan.sk_tiles > 0) {
+      const size_t ticket_bytes = (size_t)plan.tiles_p * plan.tiles_q * plan.cta_group * sizeof(int);
+      cudaError_t e = cudaMemsetAsync(scratch, 0, ticket_bytes, stream);
+      if (e != cudaSuccess) return b200::set_cuda_error(e);
+    }
+  }
+  b200_gemm_handle h;
+  rc = b200::prepare(&local, &h);
+  if (rc) return rc;
+  return b200::run(&h, stream);
+}
 
 int b200_gemm_a16w16(const b200_gemm_args* args, void* cuda_stream) {
   b200_gemm_handle h;

@@ -102,6 +102,24 @@ typedef struct b200_gemm_plan {
  * (kernels/gemm_a16w16_gfx950.py:1434-1440, kernels/common.py:7-39). */
 int b200_gemm_a16w16(const b200_gemm_args* args, void* cuda_stream);
 
+/* Same GEMM as b200_gemm_a16w16 for callers that are not allowed to allocate device memory: plug-ins running inside a
+ * serving engine or embedded runtime that owns the whole device arena, where cudaMalloc is forbidden after start-up or
+ * would fail, and that therefore cannot provide `workspace` either. It has no counterpart in the reference (whose
+ * split-K scratch is a torch allocation, kernels/gemm_a16w16_gfx950.py:1277-1281).
+ *   - `args->workspace` / `workspace_bytes` are ignored. The scratch a call needs (split-K / stream-K tickets and fp32
+ *     partial tiles, repack images) comes from one array of B200_GEMM_STATIC_SCRATCH_BYTES built into the library; every
+ *     GPU that loads the library holds that array until the process exits.
+ *   - A call whose plan needs more scratch than that returns B200_GEMM_ERR_TOO_LARGE and launches nothing
+ *     (b200_gemm_workspace_bytes tells the need beforehand). Calls that need no scratch are never limited.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs stay the caller's.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current); make that first call outside any stream capture. Later calls reuse the address.
+ *   - All calls on a device share the one array, which keeps the previous call's contents; the tickets a call uses are
+ *     cleared on its stream before its kernel runs. Two calls that overlap on the GPU (different streams, or different
+ *     host threads without stream ordering) race on the array: serialise them. */
+#define B200_GEMM_STATIC_SCRATCH_BYTES (16u << 20)
+int b200_gemm_a16w16_static_scratch(const b200_gemm_args* args, void* cuda_stream);
+
 /* Plan once, launch many times. b200_gemm_prepare does all host-side work of a call (validation, plan, tensor maps;
  * host memory only) and returns an opaque handle; b200_gemm_launch enqueues the kernels of that call on a stream of
  * the device that was current at prepare time; b200_gemm_release frees the handle. The handle stays valid while the
