@@ -73,7 +73,8 @@ static const Variant* find_variant(int tile_q, int cta_group) {
 }
 
 static int dyn_smem_bytes(int tile_q, int stages, int cta_group) {
-  return stages * (kUStageBytes + (tile_q / cta_group) * kTileK * 2) + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024;
+  const int staging = tile_q >= 64 ? 4 * 2 * 32 * 128 : 0;
+  return stages * (kUStageBytes + (tile_q / cta_group) * kTileK * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024;
 }
 
 struct DeviceInfo {
@@ -357,10 +358,31 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   if (rc) return rc;
   p.out = a->out;
   p.bias = a->bias;
+  {
+    // Finished tiles leave through TMA stores when C's rows are 16-byte aligned (and D is not written transposed).
+    const int es = a->out_dtype == B200_GEMM_DTYPE_FP32 ? 4 : 2;
+    p.tma_store = 0;
+    if (!pl.swap_ab && pl.tile_n >= 64 && (reinterpret_cast<uintptr_t>(a->out) & 15) == 0 && ((a->ldo * es) & 15) == 0) {
+      EncodeTiledFn enc = get_encode_fn();
+      if (enc == nullptr) return B200_GEMM_ERR_DRIVER;
+      const CUtensorMapDataType dt = a->out_dtype == B200_GEMM_DTYPE_FP32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                     : a->out_dtype == B200_GEMM_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+      cuuint64_t dims[2] = {(cuuint64_t)a->n, (cuuint64_t)a->m};
+      cuuint64_t strides[1] = {(cuuint64_t)a->ldo * es};
+      cuuint32_t box[2] = {(cuuint32_t)(128 / es), 32};
+      cuuint32_t estr[2] = {1, 1};
+      if (enc(&p.tmap_out, dt, 2, a->out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+        p.tma_store = 1;
+    }
+  }
   p.tickets = reinterpret_cast<int*>(ws);
   p.partials = reinterpret_cast<float*>(ws + r.off_partials);
   p.status = a->status;
-  p.trace = (a->trace != nullptr && a->trace_words >= (uint64_t)pl.grid * kTraceRoles * kTraceItems * kTraceStamps) ? reinterpret_cast<unsigned long long*>(a->trace) : nullptr;
+  const uint64_t trace_need = (uint64_t)pl.grid * kTraceRoles * kTraceItems * kTraceStamps;
+  p.trace = (a->trace != nullptr && a->trace_words >= trace_need) ? reinterpret_cast<unsigned long long*>(a->trace) : nullptr;
+  p.trace_detail = (p.trace != nullptr && a->trace_words >= 2 * trace_need) ? 1 : 0;
   p.ldo = a->ldo;
   p.P = r.P, p.Q = r.Q, p.K = (int)a->k;
   p.tiles_p = pl.tiles_p, p.tiles_q = pl.tiles_q, p.num_tiles = pl.tiles_p * pl.tiles_q;

@@ -33,12 +33,14 @@ constexpr int kUStageBytes = kTileP * kTileK * 2;  // 16 KB
 struct alignas(64) GemmParams {
   CUtensorMap tmap_u;
   CUtensorMap tmap_v;
+  CUtensorMap tmap_out;  // output, box = 32 rows x 128 bytes (valid when tma_store != 0)
   void* out;
   const void* bias;
   float* partials;  // [tile][slice][chunk][128][CW] fp32
   int* tickets;     // [tile]
   int* status;      // int32[4] or null
   unsigned long long* trace;  // optional timeline: [cta][role 0..3][item 0..15][4] stamps / counters, or null
+  int trace_detail;           // 1: also count cycles per K block in the MMA warp (slows the kernel down)
   long long ldo;    // output row stride (elements)
   int P, Q, K;
   int tiles_p, tiles_q, num_tiles;
@@ -49,6 +51,7 @@ struct alignas(64) GemmParams {
   int sk_slots;     // stream-K: partial-tile slots reserved per tile (upper bound of contributors)
   int group_p;      // grouped rasterisation over tile rows of P (0 = off)
   int swap_out;     // 1: D^T is written (out[q*ldo + p]); bias indexed by p
+  int tma_store;    // 1: finished tiles leave through swizzled staging smem and TMA stores (needs 16-byte aligned C rows)
   int out_dtype;    // 1 fp32, 2 bf16, 3 fp16
   int in_dtype;     // 2 bf16, 3 fp16
   int u_mn_major;   // 1: U is P-contiguous, loaded as two [64 P x 64 K] boxes
@@ -150,7 +153,11 @@ struct SmemLayout {
   static constexpr int kVStageBytes = kVRows * kTileK * 2;
   static constexpr int kStageBytes = kUStageBytes + kVStageBytes;
   static constexpr int kRingBytes = STAGES * kStageBytes;
-  static constexpr int kBiasOff = kRingBytes;            // float[256]
+  // Epilogue staging for TMA stores: per epilogue warp two 32-row x 128-byte swizzled images (tiles >= 64 wide only).
+  static constexpr int kStageOutBytes = 32 * 128;
+  static constexpr int kOutOff = kRingBytes;
+  static constexpr int kOutBytes = TILE_Q >= 64 ? 4 * 2 * kStageOutBytes : 0;
+  static constexpr int kBiasOff = kOutOff + kOutBytes;   // float[256]
   static constexpr int kBarOff = kBiasOff + 256 * 4;     // full[S], empty[S], acc_full[2], acc_empty[2]
   static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;  // tmem ptr, abort flag, last flag
   static constexpr int kTotal = kMiscOff + 16;
@@ -295,6 +302,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
     fence_mbar_init();
     prefetch_tmap(&p.tmap_u);
     prefetch_tmap(&p.tmap_v);
+    if (p.tma_store) prefetch_tmap(&p.tmap_out);
   }
   if (warp == 1) {
     tmem_alloc<CG>(smem_u32(const_cast<uint32_t*>(tmem_ptr_s)), kTmemCols);
@@ -326,7 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         trace_stamp(p, 0, item, 0);
         int stalls = 0;
         for (int kb = w.kb0; kb < w.kb0 + w.kbn; ++kb) {
-          if (p.trace != nullptr && !mbar_try_wait(empty_bar(stage), phase ^ 1u)) ++stalls;
+          if (p.trace != nullptr && p.trace_detail != 0 && !mbar_try_wait(empty_bar(stage), phase ^ 1u)) ++stalls;
           if (!mbar_wait<CG == 2>(empty_bar(stage), phase ^ 1u, abort_s)) {
             report_abort(p, 0, u);
             ok = false;
@@ -400,7 +408,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       WorkIter wi;
       wi.init(p, walker, walkers);
       Unit w;
-      const bool tracing = p.trace != nullptr;
+      const bool tracing = p.trace != nullptr && p.trace_detail != 0;
+      // `ready` = the full barrier of the stage about to be consumed was already seen complete (probed one K block
+      // ahead, so that the probe's latency hides behind the MMA issue of the block before).
+      int ready = 0;
       for (; ok && wi.next(p, w); ++it) {
         const int u = w.tile;
         const int buf = it & 1;
@@ -420,15 +431,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         for (int kb = 0; kb < w.kbn; ++kb) {
           long long c0 = 0, c1 = 0, c3 = 0;
           if (tracing) c0 = clock64();
-          if (lane == 0) {
-            if (tracing && !mbar_try_wait(full_bar(stage), phase)) ++stalls;
-            good = mbar_wait<CG == 2>(full_bar(stage), phase, abort_s) ? 1 : 0;
-          }
-          good = __shfl_sync(0xffffffffu, good, 0);
-          if (!good) {
-            if (lane == 0) report_abort(p, 2, u);
-            ok = false;
-            break;
+          if (!ready) {
+            if (lane == 0) {
+              ++stalls;
+              good = mbar_wait<CG == 2>(full_bar(stage), phase, abort_s) ? 1 : 0;
+            }
+            good = __shfl_sync(0xffffffffu, good, 0);
+            if (!good) {
+              if (lane == 0) report_abort(p, 2, u);
+              ok = false;
+              break;
+            }
           }
           tc_fence_after();
           if (tracing) c1 = clock64();
@@ -437,6 +450,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
           const uint32_t sv = su + kUStageBytes;
           const uint64_t du = (uint64_t(p.u_desc_hi) << 32) | uint64_t(p.u_desc_lo | ((su >> 4) & 0x3fffu));
           const uint64_t dv = (uint64_t(p.v_desc_hi) << 32) | uint64_t(p.v_desc_lo | ((sv >> 4) & 0x3fffu));
+          // Probe the next stage now; the answer is collected after the MMAs below have been issued.
+          const int nstage = stage + 1 == STAGES ? 0 : stage + 1;
+          const uint32_t nphase = stage + 1 == STAGES ? phase ^ 1u : phase;
+          int next_ready = 0;
+          if (lane == 0) next_ready = mbar_try_wait(full_bar(nstage), nphase) ? 1 : 0;
           if (elect_one()) {
 #pragma unroll
             for (int j = 0; j < kTileK / kUmmaK; ++j) {
@@ -456,18 +474,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
               c_wait += c1 - c0, c_mma += c3 - c1, c_commit += c4 - c3;
             }
           }
-          __syncwarp();
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          ready = __shfl_sync(0xffffffffu, next_ready, 0);
+          stage = nstage;
+          phase = nphase;
         }
         if (elect_one()) {
           trace_stamp(p, 1, it, 2);
           trace_value(p, 1, it, 3, stalls);
-          trace_value(p, 3, it, 0, c_wait);
-          trace_value(p, 3, it, 2, c_mma);
-          trace_value(p, 3, it, 3, c_commit);
+          if (tracing) {
+            trace_value(p, 3, it, 0, c_wait);
+            trace_value(p, 3, it, 2, c_mma);
+            trace_value(p, 3, it, 3, c_commit);
+          }
           if (ok) {  // accumulator complete: wake the epilogue of every CTA of the pair
             if constexpr (CG == 2) {
               umma_commit_pair(mapa_cluster(accf_bar(buf), 0));
@@ -486,6 +504,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
     const int row = quarter * 32 + lane;
     const int et = threadIdx.x - 64;  // 0..127
     int it = 0;
+    int out_flip = 0;  // which of the warp's two staging images the next TMA store uses
     WorkIter wi;
     wi.init(p, walker, walkers);
     Unit w;
@@ -525,29 +544,94 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       float4* part = nullptr;
       if (!direct) part = reinterpret_cast<float4*>(p.partials) + (size_t)(w.slot * CG + rank) * kSlotVec + row;
 
-#pragma unroll 1
-      for (int c = 0; c < NCHUNK; ++c) {
-        uint32_t r[32];
+      // Two register buffers: the tcgen05.ld of chunk c+1 is in flight while chunk c is converted and stored.
+      auto load_chunk = [&](uint32_t(&r)[32], int c) {
         if constexpr (CW == 32)
           tmem_ld_32x32(t_acc + c * CW, r);
         else
           tmem_ld_32x16(t_acc + c * CW, r);
-        tmem_ld_wait();
-        if (c == NCHUNK - 1) {
-          // Everything this warp needs is in registers: hand the accumulator back to the MMA thread.
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) {
-            if (CG == 2 && rank != 0)
-              mbar_arrive_cluster(acce_bar(buf), 0);
-            else
-              mbar_arrive(acce_bar(buf));
-          }
+      };
+      auto release_acc = [&]() {
+        // Everything this warp needs is in registers: hand the accumulator back to the MMA thread.
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (CG == 2 && rank != 0)
+            mbar_arrive_cluster(acce_bar(buf), 0);
+          else
+            mbar_arrive(acce_bar(buf));
         }
+      };
+      // TMA-store path: bias + cast, then this lane's row segment goes into the warp's swizzled staging image
+      // (16-byte chunk j of row t sits at position j ^ (t % 8)); every full 128-byte row image is stored by one lane.
+      const bool staged = direct && p.tma_store != 0 && TILE_Q >= 64;
+      const uint32_t out_stage0 = base + L::kOutOff + (uint32_t)(warp - 2) * (2 * L::kStageOutBytes);
+      auto stage_flush = [&](int col0) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        const int row0 = (w.tp * CG + rank) * kTileP + quarter * 32;
+        if (lane == 0) {
+          // a box that starts outside C holds nothing to write; one that straddles the edge is clipped by TMA
+          if (row0 < p.P && col0 < p.Q)
+            tma_store_2d(&p.tmap_out, col0, row0, out_stage0 + (uint32_t)(out_flip & 1) * L::kStageOutBytes);
+          tma_store_commit();
+        }
+        ++out_flip;
+      };
+      auto stage_acquire = [&]() {
+        // the store issued two flushes ago has finished reading the buffer about to be overwritten
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+      };
+      auto process_chunk = [&](uint32_t(&r)[32], int c) {
         float v[CW];
 #pragma unroll
         for (int i = 0; i < CW; ++i) v[i] = __uint_as_float(r[i]);
-        if (direct) {
+        if (staged) {
+          if constexpr (CW == 32) {
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int i = 0; i < CW; ++i) v[i] += bias_s[c * CW + i];
+            }
+            const uint32_t row_base = out_stage0 + (uint32_t)(out_flip & 1) * L::kStageOutBytes + (uint32_t)lane * 128u;
+            if (p.out_dtype == 1) {
+              stage_acquire();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const uint32_t addr = row_base + (uint32_t)((j ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]),
+                             "f"(v[4 * j + 3])
+                             : "memory");
+              }
+              stage_flush(qbase + c * CW);
+            } else {
+              if ((c & 1) == 0) stage_acquire();
+              uint32_t pk[16];
+              if (p.out_dtype == 2) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(v[i], v[i + 1]);
+                  pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                  __half2 h = __floats2half2_rn(v[i], v[i + 1]);
+                  pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int jj = (c & 1) * 4 + j;
+                const uint32_t addr = row_base + (uint32_t)((jj ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * j]), "r"(pk[4 * j + 1]), "r"(pk[4 * j + 2]),
+                             "r"(pk[4 * j + 3])
+                             : "memory");
+              }
+              if (c & 1) stage_flush(qbase + (c - 1) * CW);
+            }
+          }
+        } else if (direct) {
           finalize_chunk<CW>(p, v, prow, qbase + c * CW, bias_s + c * CW, bias_p);
         } else {
           // slot layout [chunk][4-column group][row][4]: one warp store covers 512 contiguous bytes
@@ -555,6 +639,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
 #pragma unroll
           for (int j = 0; j < CW / 4; ++j)
             __stcg(dst + j * kTileP, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+        }
+      };
+      {
+        uint32_t ra[32], rb[32];
+        load_chunk(ra, 0);
+        tmem_ld_wait();
+#pragma unroll 1
+        for (int c = 0; c < NCHUNK; c += 2) {
+          if (c + 1 < NCHUNK)
+            load_chunk(rb, c + 1);
+          else
+            release_acc();
+          process_chunk(ra, c);
+          if (c + 1 < NCHUNK) {
+            tmem_ld_wait();
+            if (c + 2 < NCHUNK)
+              load_chunk(ra, c + 2);
+            else
+              release_acc();
+            process_chunk(rb, c + 1);
+            if (c + 2 < NCHUNK) tmem_ld_wait();
+          }
         }
       }
 
@@ -612,6 +718,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       }
       if (et == 0) trace_stamp(p, 2, it, 2);
     }
+    if (lane == 0) tma_store_wait_all<0>();  // staging smem and C must be complete before the CTA leaves
   }
 
   // ---------------------------------------------------------------------- teardown

@@ -53,7 +53,8 @@ class Policy:
 def smem_bytes(tile_n: int, stages: int, cta_group: int = 1) -> int:
     """Dynamic shared memory of one CTA: the ring, the bias slice, the barriers and alignment slack. In a pair
     each CTA holds 128 of the tile's 256 rows and half of its tile_n columns."""
-    return stages * (TILE_M * TILE_K * 2 + (tile_n // cta_group) * TILE_K * 2) + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024
+    staging = 4 * 2 * 32 * 128 if tile_n >= 64 else 0  # epilogue images for TMA stores
+    return stages * (TILE_M * TILE_K * 2 + (tile_n // cta_group) * TILE_K * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024
 
 
 def split_k_slices(k: int, split_k: int) -> list[tuple[int, int]]:

@@ -81,7 +81,8 @@ typedef struct b200_gemm_args {
                       producer / MMA / epilogue roles for its first 16 work items: [cta][role 0..3][item][4] (begin, first
                       data / accumulator handed back, end, and a counter: stalled waits, or clock64 for the epilogue;
                       role 3 = cycles the MMA thread spent in wait / fence / issue / commit). Needs
-                      grid * 4 * 16 * 4 words; ignored when smaller                                            */
+                      grid * 4 * 16 * 4 words; ignored when smaller; twice that many words also turns on the
+                      per-K-block cycle counters (which slow the kernel down)                                            */
   uint64_t trace_words;
 } b200_gemm_args;
 
