@@ -74,6 +74,7 @@ class Plan(C.Structure):
         ("grid", C.c_int32),
         ("smem_bytes", C.c_int32),
         ("tmem_cols", C.c_int32),
+        ("cluster_split", C.c_int32),
         ("stream_k", C.c_int32),
         ("sk_tiles", C.c_int32),
         ("sk_slots", C.c_int32),

@@ -73,7 +73,9 @@ static const Variant* find_variant(int tile_q, int cta_group) {
 }
 
 static int dyn_smem_bytes(int tile_q, int stages, int cta_group) {
-  const int staging = tile_q >= 64 ? 4 * 2 * 32 * 128 : 0;
+  const int staging0 = tile_q >= 64 ? 4 * 2 * 32 * 128 : 0;
+  const int recv = tile_q <= 64 ? kTileP * tile_q * 4 : 0;
+  const int staging = recv > staging0 ? recv : staging0;
   return stages * (kUStageBytes + (tile_q / cta_group) * kTileK * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024;
 }
 
@@ -217,14 +219,26 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
     }
   }
 
-  const bool tickets = pl.split_k > 1 || pl.sk_tiles > 0;
+  // Cluster split-K: the K slices of a tile are the CTAs of one thread-block cluster and reduce through distributed
+  // shared memory: no workspace, no tickets. One tile per cluster, so the grid is not persistent.
+  pl.cluster_split = 0;
+  if (pol.split_mode == B200_GEMM_SPLIT_CLUSTER && pl.split_k > 1 && !pl.stream_k) {
+    if (pl.cta_group != 1 || pl.tile_n > 64) return B200_GEMM_ERR_BAD_POLICY;
+    int s = 16;
+    while (s > pl.split_k) s >>= 1;  // largest power of two <= split_k (split_k was clamped to the K blocks)
+    pl.split_k = s;
+    pl.num_units = (int)(tiles * s);
+    pl.grid = pl.num_units;
+    pl.cluster_split = s > 1 ? s : 0;
+  }
+  const bool tickets = (pl.split_k > 1 && pl.cluster_split == 0) || pl.sk_tiles > 0;
   if (tickets && tiles * pl.cta_group > (int64_t)(kCounterBytes / 4)) return B200_GEMM_ERR_TOO_LARGE;
   // The ticket region has a fixed size and is reserved by every call that uses the workspace at all, so that no call
   // ever writes partial sums or a repack image where another call keeps its tickets.
   pl.counter_bytes = (tickets || pl.a_repacked || pl.b_repacked) ? kCounterBytes : 0;
   pl.partial_bytes = pl.sk_tiles > 0 ? (uint64_t)pl.sk_tiles * pl.sk_slots * pl.tile_m * pl.tile_n * 4
-                     : pl.split_k > 1 ? (uint64_t)pl.num_units * pl.tile_m * pl.tile_n * 4
-                                      : 0;
+                     : (pl.split_k > 1 && pl.cluster_split == 0) ? (uint64_t)pl.num_units * pl.tile_m * pl.tile_n * 4
+                                                                 : 0;
   const uint64_t ra = pl.a_repacked ? round_up((uint64_t)a_rows * r->ra_ld * 2, 256) : 0;
   const uint64_t rb = pl.b_repacked ? round_up((uint64_t)b_rows * r->rb_ld * 2, 256) : 0;
   pl.repack_bytes = ra + rb;
@@ -296,7 +310,7 @@ struct RepackJob {
 struct b200_gemm_handle {
   b200::GemmParams params;
   b200::KernelFn fn;
-  int grid, smem_bytes, device, cta_group;
+  int grid, smem_bytes, device, cta_group, cluster_split;
   int n_repack;
   b200::RepackJob repack[2];
   b200_gemm_plan plan;
@@ -348,7 +362,6 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
 
   GemmParams& p = h->params;
   memset(&p, 0, sizeof(p));
-  const b200_gemm_policy& pol = a->policy;
   const void* u_ptr = pl.swap_ab ? pb : pa;
   const void* v_ptr = pl.swap_ab ? pa : pb;
   const int64_t u_ld = pl.swap_ab ? ldb : lda, v_ld = pl.swap_ab ? lda : ldb;
@@ -388,6 +401,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   p.tiles_p = pl.tiles_p, p.tiles_q = pl.tiles_q, p.num_tiles = pl.tiles_p * pl.tiles_q;
   p.kb_total = (int)((a->k + kTileK - 1) / kTileK);
   p.split_k = pl.split_k;
+  p.cluster_split = pl.cluster_split;
   p.num_units = pl.num_units;
   p.sk_tiles = pl.sk_tiles;
   p.sk_slots = pl.sk_slots;
@@ -406,6 +420,12 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   h->grid = pl.grid;
   h->smem_bytes = pl.smem_bytes;
   h->cta_group = pl.cta_group;
+  h->cluster_split = pl.cluster_split;
+  if (pl.cluster_split > 8) {
+    // clusters of 16 CTAs are outside the portable range: the kernel has to opt in
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(h->fn), cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return set_cuda_error(e);
+  }
   {
     std::lock_guard<std::mutex> lock(g_dev_mutex);
     if (!dev->attr_set[vi][pl.stages]) {
@@ -430,9 +450,9 @@ static int run(const b200_gemm_handle* h, cudaStream_t stream) {
   cfg.dynamicSmemBytes = h->smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
-  if (h->cta_group == 2) {
+  if (h->cta_group == 2 || h->cluster_split > 1) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.x = h->cta_group == 2 ? 2 : h->cluster_split;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;

@@ -46,6 +46,7 @@ struct alignas(64) GemmParams {
   int tiles_p, tiles_q, num_tiles;
   int kb_total;  // ceil(K / 64)
   int split_k;
+  int cluster_split;  // > 1: the split_k CTAs of a tile form one thread-block cluster and reduce through DSMEM
   int num_units;
   int sk_tiles;     // stream-K: the first sk_tiles tiles are cut into equal K spans over all CTAs (0 = off)
   int sk_slots;     // stream-K: partial-tile slots reserved per tile (upper bound of contributors)
@@ -156,7 +157,10 @@ struct SmemLayout {
   // Epilogue staging for TMA stores: per epilogue warp two 32-row x 128-byte swizzled images (tiles >= 64 wide only).
   static constexpr int kStageOutBytes = 32 * 128;
   static constexpr int kOutOff = kRingBytes;
-  static constexpr int kOutBytes = TILE_Q >= 64 ? 4 * 2 * kStageOutBytes : 0;
+  // The same region receives the other CTAs' rows in cluster split-K mode: float[S][128/S][TILE_Q] (TILE_Q <= 64).
+  static constexpr int kRecvBytes = TILE_Q <= 64 ? kTileP * TILE_Q * 4 : 0;
+  static constexpr int kStagingBytes = TILE_Q >= 64 ? 4 * 2 * kStageOutBytes : 0;
+  static constexpr int kOutBytes = kRecvBytes > kStagingBytes ? kRecvBytes : kStagingBytes;
   static constexpr int kBiasOff = kOutOff + kOutBytes;   // float[256]
   static constexpr int kBarOff = kBiasOff + 256 * 4;     // full[S], empty[S], acc_full[2], acc_empty[2]
   static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;  // tmem ptr, abort flag, last flag
@@ -310,7 +314,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
   }
   tc_fence_before();
   __syncthreads();
-  if constexpr (CG == 2) {  // the peer's barriers must exist before anything is signalled across the pair
+  const bool cluster_mode = CG == 1 && p.cluster_split > 1;
+  if (CG == 2 || cluster_mode) {  // every CTA of the cluster is running before anything is sent across it
     cluster_arrive();
     cluster_wait();
   }
@@ -319,7 +324,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (one per CTA)
-    if (lane == 0) {
+    // Like the MMA warp, the whole warp walks the loop (uniform operands); lane 0 polls, one elected lane issues.
+    {
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0;
@@ -328,71 +334,79 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       wi.init(p, walker, walkers);
       Unit w;
       int item = 0;
+      // In the first pass over the ring every stage is free: no need to ask its barrier.
       for (; ok && wi.next(p, w); ++item) {
         const int u = w.tile;
         const int p0 = (w.tp * CG + rank) * kTileP, q0 = w.tq * TILE_Q + rank * kVRows;
-        trace_stamp(p, 0, item, 0);
-        int stalls = 0;
+        if (lane == 0) trace_stamp(p, 0, item, 0);
         for (int kb = w.kb0; kb < w.kb0 + w.kbn; ++kb) {
-          if (p.trace != nullptr && p.trace_detail != 0 && !mbar_try_wait(empty_bar(stage), phase ^ 1u)) ++stalls;
-          if (!mbar_wait<CG == 2>(empty_bar(stage), phase ^ 1u, abort_s)) {
-            report_abort(p, 0, u);
-            ok = false;
-            break;
+          if (issued >= STAGES) {
+            int good = 1;
+            if (lane == 0) good = mbar_wait<CG == 2>(empty_bar(stage), phase ^ 1u, abort_s) ? 1 : 0;
+            good = __shfl_sync(0xffffffffu, good, 0);
+            if (!good) {
+              if (lane == 0) report_abort(p, 0, u);
+              ok = false;
+              break;
+            }
           }
-          if (kb == w.kb0) trace_stamp(p, 0, item, 1);
+          if (kb == w.kb0 && lane == 0) trace_stamp(p, 0, item, 1);
           // Data of both CTAs of a pair is counted on the leader's barrier, which the MMA thread waits on.
           uint32_t fb = full_bar(stage);
           if constexpr (CG == 2) fb = mapa_cluster(fb, 0);
-          if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), kTxBytes);
           const uint32_t su = base + stage * L::kStageBytes;
           const uint32_t sv = su + kUStageBytes;
           const int k0 = kb * kTileK;
-          auto load = [&](uint32_t dst, const void* map, int x, int y) {
-            if constexpr (CG == 2)
-              tma_load_2d_pair(dst, map, x, y, fb);
-            else
-              tma_load_2d(dst, map, x, y, fb);
-          };
-          if (!p.u_mn_major) {
-            load(su, &p.tmap_u, k0, p0);
-          } else {
-            load(su, &p.tmap_u, p0, k0);
-            load(su + 8192u, &p.tmap_u, p0 + 64, k0);
-          }
-          if (!p.v_mn_major) {
-            load(sv, &p.tmap_v, k0, q0);
-          } else {
+          if (elect_one()) {
+            if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), kTxBytes);
+            auto load = [&](uint32_t dst, const void* map, int x, int y) {
+              if constexpr (CG == 2)
+                tma_load_2d_pair(dst, map, x, y, fb);
+              else
+                tma_load_2d(dst, map, x, y, fb);
+            };
+            if (!p.u_mn_major) {
+              load(su, &p.tmap_u, k0, p0);
+            } else {
+              load(su, &p.tmap_u, p0, k0);
+              load(su + 8192u, &p.tmap_u, p0 + 64, k0);
+            }
+            if (!p.v_mn_major) {
+              load(sv, &p.tmap_v, k0, q0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < (kVRows >= 64 ? kVRows / 64 : 1); ++j) load(sv + 8192u * j, &p.tmap_v, q0 + 64 * j, k0);
+              for (int j = 0; j < (kVRows >= 64 ? kVRows / 64 : 1); ++j) load(sv + 8192u * j, &p.tmap_v, q0 + 64 * j, k0);
+            }
           }
+          __syncwarp();
           ++issued;
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        trace_stamp(p, 0, item, 2);
-        trace_value(p, 0, item, 3, stalls);
+        if (lane == 0) trace_stamp(p, 0, item, 2);
       }
-      if (!ok && CG == 1) {
-        // Loads already issued still write this CTA's smem: give each one a bounded chance to land.
-        const int pending = issued < STAGES ? issued : STAGES;
-        for (int i = 0; i < pending; ++i) {
-          int s = stage - 1 - i;
-          uint32_t ph = phase;
-          if (s < 0) {
-            s += STAGES;
-            ph ^= 1u;
+      if (!ok && lane == 0) {
+        if (CG == 1) {
+          // Loads already issued still write this CTA's smem: give each one a bounded chance to land.
+          const int pending = issued < STAGES ? issued : STAGES;
+          for (int i = 0; i < pending; ++i) {
+            int s = stage - 1 - i;
+            uint32_t ph = phase;
+            if (s < 0) {
+              s += STAGES;
+              ph ^= 1u;
+            }
+            const unsigned long long t0 = globaltimer_ns();
+            while (!mbar_try_wait(full_bar(s), ph) && globaltimer_ns() - t0 < 100000000ull) {
+            }
           }
+        } else {
+          // In a pair the byte counts live on the leader's barriers: wait a fixed, bounded time instead.
           const unsigned long long t0 = globaltimer_ns();
-          while (!mbar_try_wait(full_bar(s), ph) && globaltimer_ns() - t0 < 100000000ull) {
+          while (globaltimer_ns() - t0 < 1000000ull) {
           }
-        }
-      } else if (!ok) {
-        // In a pair the byte counts live on the leader's barriers: wait a fixed, bounded time instead.
-        const unsigned long long t0 = globaltimer_ns();
-        while (globaltimer_ns() - t0 < 1000000ull) {
         }
       }
     }
@@ -562,6 +576,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
             mbar_arrive(acce_bar(buf));
         }
       };
+      uint32_t cl_dst = 0;
+      if (cluster_mode) {
+        const int rows_per_cta = kTileP / p.cluster_split;
+        const uint32_t local = base + L::kOutOff +
+                               (uint32_t)(((int)cluster_ctarank() * rows_per_cta + row % rows_per_cta) * TILE_Q) * 4u;
+        cl_dst = mapa_cluster(local, (uint32_t)(row / rows_per_cta));
+      }
       // TMA-store path: bias + cast, then this lane's row segment goes into the warp's swizzled staging image
       // (16-byte chunk j of row t sits at position j ^ (t % 8)); every full 128-byte row image is stored by one lane.
       const bool staged = direct && p.tma_store != 0 && TILE_Q >= 64;
@@ -633,6 +654,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
           }
         } else if (direct) {
           finalize_chunk<CW>(p, v, prow, qbase + c * CW, bias_s + c * CW, bias_p);
+        } else if (cluster_mode) {
+          // cluster split-K: this row's partial sums go to the CTA that owns the row, into slab [my rank][row % R]
+#pragma unroll
+          for (int j = 0; j < CW / 4; ++j)
+            asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cl_dst + (uint32_t)(c * CW + 4 * j) * 4u), "f"(v[4 * j]),
+                         "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                         : "memory");
         } else {
           // slot layout [chunk][4-column group][row][4]: one warp store covers 512 contiguous bytes
           float4* dst = part + (size_t)c * (CW / 4) * kTileP;
@@ -665,7 +693,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       }
 
       if (et == 0) trace_stamp(p, 2, it, 1);
-      if (!direct) {
+      if (!direct && !cluster_mode) {
         // Ticket: the CTA that arrives last at this (half-)tile sums all contributions in slot order.
         __threadfence();
         named_bar_sync(2, kEpiThreads);
@@ -724,9 +752,42 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  if constexpr (CG == 2) {  // no CTA of a pair leaves while its peer may still signal it or use its TMEM half
+  if (CG == 2 || cluster_mode) {
+    // pair: no CTA leaves while its peer may still signal it or use its TMEM half;
+    // cluster split-K: every CTA's rows have arrived in their owner's shared memory
     cluster_arrive();
     cluster_wait();
+  }
+  if constexpr (CG == 1 && TILE_Q <= 64) {
+    if (cluster_mode && warp >= 2) {
+      // Each CTA owns 128/S rows of the tile: sum the S slabs in rank order (deterministic), bias, cast, store.
+      const int S = p.cluster_split, R = kTileP / S;
+      const int crank = (int)cluster_ctarank();
+      const int tile = (int)blockIdx.x / S;
+      int tp, tq;
+      raster_tile(p, tile, tp, tq);
+      const float* recv = reinterpret_cast<const float*>(sm + L::kOutOff);
+      const int et = threadIdx.x - 64;
+      for (int e = et; e < R * TILE_Q; e += kEpiThreads) {
+        // D^T output: consecutive threads take consecutive rows (contiguous in memory); else consecutive columns
+        const int lrow = p.swap_out ? e % R : e / TILE_Q;
+        const int col = p.swap_out ? e / R : e % TILE_Q;
+        float acc = 0.f;
+        for (int src = 0; src < S; ++src) acc += recv[(src * R + lrow) * TILE_Q + col];
+        const int prow = tp * kTileP + crank * R + lrow;
+        const int q = tq * TILE_Q + col;
+        if (prow < p.P && q < p.Q) {
+          if (p.bias != nullptr) acc += load_in_as_float(p.bias, p.swap_out ? prow : q, p.in_dtype);
+          const long long idx = p.swap_out ? (long long)q * p.ldo + prow : (long long)prow * p.ldo + q;
+          if (p.out_dtype == 1)
+            reinterpret_cast<float*>(p.out)[idx] = acc;
+          else if (p.out_dtype == 2)
+            reinterpret_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(acc);
+          else
+            reinterpret_cast<__half*>(p.out)[idx] = __float2half_rn(acc);
+        }
+      }
+    }
   }
   if (warp == 1) {
     __syncwarp();

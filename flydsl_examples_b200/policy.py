@@ -31,7 +31,7 @@ REFERENCE_KEYS = (
 # Keys that only exist here.
 BLACKWELL_KEYS = ("tile_n", "swap_ab", "cta_group", "split_mode", "max_ctas", "stream_k")
 CONTROL_KEYS = ("strict_reference_envelope",)
-SPLIT_MODES = {"ticket": 0, "atomic": 1}
+SPLIT_MODES = {"ticket": 0, "cluster": 2}
 
 
 @dataclass(frozen=True)
@@ -54,6 +54,7 @@ def smem_bytes(tile_n: int, stages: int, cta_group: int = 1) -> int:
     """Dynamic shared memory of one CTA: the ring, the bias slice, the barriers and alignment slack. In a pair
     each CTA holds 128 of the tile's 256 rows and half of its tile_n columns."""
     staging = 4 * 2 * 32 * 128 if tile_n >= 64 else 0  # epilogue images for TMA stores
+    staging = max(staging, TILE_M * tile_n * 4 if tile_n <= 64 else 0)  # rows received in cluster split-K mode
     return stages * (TILE_M * TILE_K * 2 + (tile_n // cta_group) * TILE_K * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024
 
 
@@ -145,6 +146,8 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
         return f"split_mode must be one of {tuple(SPLIT_MODES)}, got {pol.split_mode!r}"
     if pol.group_m < 0:
         return f"group_m must be >= 0, got {pol.group_m}"
+    if pol.split_mode == "cluster" and pol.split_k > 1 and (pol.cta_group != 1 or pol.tile_n > 64 or pol.stream_k):
+        return "cluster split-K needs cta_group 1, tile_n <= 64 and no stream_k"
     # The operand on the MMA N axis, when it is contiguous along N (or M after a swap), is fetched as 64-wide boxes.
     a_mn = layout[0] == "t"
     b_mn = layout[1] == "n"
@@ -164,17 +167,24 @@ _KBLOCK_CYCLES = {(1, 256): 512 / 0.72, (2, 256): 512 / 0.87, (1, 128): 340.0, (
 _FIXED_CYCLES = 6000.0  # launch tail, pipeline fill, last epilogue
 
 
-def _auto_split(tiles: int, kb: int, walkers: int) -> int:
-    """K slices per tile when the tiles alone cannot occupy the machine."""
+def _auto_split(tiles: int, kb: int, walkers: int, cluster_ok: bool = False) -> tuple[int, str]:
+    """(K slices per tile, reduction mode) when the tiles alone cannot occupy the machine. Narrow single-CTA tiles
+    reduce inside a thread-block cluster (2..16 CTAs, through distributed shared memory); the rest use tickets."""
     if tiles * 2 <= walkers and kb >= 8:
-        return max(1, min(walkers // tiles, kb // 4, 64))
-    return 1
+        if cluster_ok:
+            s = 16
+            while s > 1 and (s > walkers // tiles or s > kb // 2):
+                s //= 2
+            if s >= 2:
+                return s, "cluster"
+        return max(1, min(walkers // tiles, kb // 4, 64)), "ticket"
+    return 1, "ticket"
 
 
 def _estimate_cycles(p_ext: int, q: int, kb: int, cta_group: int, tile_n: int, num_sms: int) -> float:
     walkers = max(1, num_sms // cta_group)
     tiles = -(-p_ext // (TILE_M * cta_group)) * -(-q // tile_n)
-    split = _auto_split(tiles, kb, walkers)
+    split, _ = _auto_split(tiles, kb, walkers, cta_group == 1 and tile_n <= 64)
     waves = -(-(tiles * split) // walkers)
     epilogue = 1000.0 + 500.0 * tile_n / 256
     fixup = (1500.0 + 400.0 * split) if split > 1 else 0.0
@@ -203,9 +213,9 @@ def heuristic(m: int, n: int, k: int, layout: str = "nt", num_sms: int = NUM_SMS
         cta_group, tile_n = best
     walkers = num_sms // cta_group
     tiles = -(-p_ext // (TILE_M * cta_group)) * -(-q // tile_n)
-    split = _auto_split(tiles, kb, walkers)
+    split, mode = _auto_split(tiles, kb, walkers, cta_group == 1 and tile_n <= 64)
     group = 8 if (tiles >= 2 * walkers and not swap) else 0
-    return Policy(tile_n=tile_n, split_k=split, group_m=group, swap_ab=swap, cta_group=cta_group)
+    return Policy(tile_n=tile_n, split_k=split, group_m=group, swap_ab=swap, cta_group=cta_group, split_mode=mode)
 
 
 def from_user_kwargs(user_kwargs: dict, m: int, n: int, k: int, layout: str, num_sms: int = NUM_SMS_DEFAULT) -> Policy:
@@ -220,7 +230,7 @@ def from_user_kwargs(user_kwargs: dict, m: int, n: int, k: int, layout: str, num
     if native:
         # A Blackwell policy is taken literally: nothing the caller left out is second-guessed by the heuristic
         # except the tile, which falls back to the heuristic's choice.
-        fields.update(split_k=1, group_m=0, swap_ab=False, stages=0, cta_group=1)
+        fields.update(split_k=1, group_m=0, swap_ab=False, stages=0, cta_group=1, split_mode="ticket")
         for key in BLACKWELL_KEYS + ("stages", "split_k", "group_m"):
             if key in user_kwargs:
                 fields[key] = user_kwargs[key]

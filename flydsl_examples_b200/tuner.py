@@ -58,19 +58,23 @@ def candidate_configs(args: TuneArgs, num_sms: int = P.NUM_SMS_DEFAULT) -> list[
         walkers = num_sms // cg
         max_stages = (P.MAX_STAGES if cg == 1 else P.MAX_STAGES_PAIR)[tile_n]
         stage_opts = sorted({max_stages, max(2, max_stages - 2)})
-        splits = [(1, False)]
+        splits = [(1, False, "ticket")]
         if tiles % walkers != 0:
-            splits.append((1, True))  # stream-K
+            splits.append((1, True, "ticket"))  # stream-K
         if args.enable_split_k or tiles * 2 <= walkers:
             for s in (2, 3, 4, 6, 8, 12, 16, 24, 32, 48):
                 if s <= kb and tiles * s <= 4 * walkers:
-                    splits.append((s, False))
+                    splits.append((s, False, "ticket"))
+            if cg == 1 and tile_n <= 64:
+                for s in (2, 4, 8, 16):  # K slices as one thread-block cluster
+                    if s <= kb and tiles * s <= 2 * walkers:
+                        splits.append((s, False, "cluster"))
         groups = (0, 4, 8) if tiles >= 2 * walkers else (0,)
-        for stages, (split_k, stream_k), group_m in itertools.product(stage_opts, splits, groups):
+        for stages, (split_k, stream_k, mode), group_m in itertools.product(stage_opts, splits, groups):
             cfg = {"tile_n": tile_n, "cta_group": cg, "stages": stages, "split_k": split_k, "stream_k": stream_k,
-                   "group_m": group_m, "swap_ab": swap}
+                   "group_m": group_m, "swap_ab": swap, "split_mode": mode}
             pol = P.Policy(tile_n=tile_n, stages=stages, split_k=split_k, group_m=group_m, swap_ab=swap, cta_group=cg,
-                           stream_k=stream_k)
+                           stream_k=stream_k, split_mode=mode)
             if P.validate(pol, args.m, args.n, args.k, args.layout) is None:
                 out.append(cfg)
     if not out:

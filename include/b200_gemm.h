@@ -37,8 +37,11 @@ extern "C" {
 /* split-K reduction modes */
 #define B200_GEMM_SPLIT_TICKET 0 /* fp32 partial tiles in the workspace; the last-arriving CTA of a tile sums them in
                                     slice order, adds bias and casts once (deterministic; never waits)            */
-#define B200_GEMM_SPLIT_ATOMIC 1 /* red.global.add.f32 onto an fp32 output that slice 0 initialised ... not used
-                                    unless asked for; needs fp32 output                                          */
+#define B200_GEMM_SPLIT_ATOMIC 1  /* reserved                                                                      */
+#define B200_GEMM_SPLIT_CLUSTER 2 /* the K slices of a tile are the CTAs of one thread-block cluster (2, 4, 8 or 16);
+                                     each CTA sends its partial rows to the row's owner through distributed shared
+                                     memory, one cluster barrier, owners sum in rank order. No workspace, no tickets,
+                                     deterministic. tile_n <= 64, cta_group 1; split_k is rounded down to a power of two */
 
 /* Blackwell policy. Replaces the reference's compile-time GemmA16W16Gfx950Param
  * (kernels/gemm_a16w16_gfx950.py:33-61): block_m/n/k, stages, split_k, *_waves, group_m, HTI flag. */
@@ -92,6 +95,7 @@ typedef struct b200_gemm_plan {
   int32_t tiles_p, tiles_q; /* tile grid over (128-row operand, tile_n operand)                              */
   int32_t num_units, grid;  /* work units (tile x K-slice) and persistent CTAs                               */
   int32_t smem_bytes, tmem_cols;
+  int32_t cluster_split;                /* CTAs per cluster in cluster split-K mode, else 0                              */
   int32_t stream_k, sk_tiles, sk_slots; /* stream-K on; tiles cut into K spans; partial slots reserved per such tile */
   int32_t a_repacked, b_repacked; /* 1 when the operand is not TMA-encodable (base or pitch not 16-byte aligned)
                                      and is first copied into an aligned scratch image in the workspace        */

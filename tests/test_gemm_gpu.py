@@ -69,6 +69,36 @@ def test_config3_small_m_split_k_fp32(split_k, swap):
     run_case(O.Case(**{**case.__dict__, "user_kwargs": kw}), repeats=2)
 
 
+@pytest.mark.parametrize("split_k", [2, 4, 8, 16])
+@pytest.mark.parametrize("swap", [True, False])
+def test_config3_cluster_split_k(split_k, swap):
+    # the K slices of a tile form one thread-block cluster and reduce through distributed shared memory
+    case = O.CONFIGS["c3"]
+    kw = {"tile_n": 32 if swap else 64, "swap_ab": swap, "split_k": split_k, "split_mode": "cluster"}
+    run_case(O.Case(**{**case.__dict__, "user_kwargs": kw}), repeats=3, prefill="randn")
+
+
+CLUSTER_SPLIT = [
+    (3, 5120, 2880, {"tile_n": 16, "swap_ab": True, "split_k": 4, "split_mode": "cluster"}),
+    (17, 300, 1000, {"tile_n": 32, "swap_ab": True, "split_k": 8, "split_mode": "cluster"}),
+    (64, 64, 768, {"tile_n": 64, "split_k": 4, "split_mode": "cluster"}),
+    (129, 136, 1536, {"tile_n": 64, "split_k": 16, "split_mode": "cluster"}),
+    (48, 5120, 2880, {"tile_n": 64, "swap_ab": True, "split_k": 2, "split_mode": "cluster"}),
+    (200, 328, 333, {"tile_n": 32, "split_k": 16, "split_mode": "cluster"}),   # 6 K blocks: rounds down to 4 slices
+]
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("idx", range(len(CLUSTER_SPLIT)))
+def test_cluster_split_k_shapes(dtype, idx):
+    m, n, k, kw = CLUSTER_SPLIT[idx]
+    for out_dtype in (None, "fp32"):
+        run_case(O.Case("cluster", dtype, "nt", m, n, k, seed=500 + idx, bias_std=0.5, out_dtype=out_dtype, user_kwargs=kw),
+                 repeats=2, prefill="randn")
+    if kw["tile_n"] >= 64:  # operands contiguous along M / N need 64-wide boxes on the tile_n side
+        run_case(O.Case("cluster_tn", dtype, "tn" if not kw.get("swap_ab") else "nn", m, n, k, seed=600 + idx, bias_std=0.5, user_kwargs=kw))
+
+
 def test_config3_default_policy():
     run_case(O.CONFIGS["c3"], repeats=5, prefill="randn")
 

@@ -11,7 +11,7 @@ def test_candidates_are_valid_and_cover_the_variant_table():
     assert cfgs
     for c in cfgs:
         pol = P.Policy(tile_n=c["tile_n"], stages=c["stages"], split_k=c["split_k"], group_m=c["group_m"], swap_ab=c["swap_ab"],
-                       cta_group=c["cta_group"], stream_k=c["stream_k"])
+                       cta_group=c["cta_group"], stream_k=c["stream_k"], split_mode=c["split_mode"])
         assert P.validate(pol, args.m, args.n, args.k, args.layout) is None
     assert any(c["cta_group"] == 2 and c["tile_n"] == 256 for c in cfgs)
     assert any(c["stream_k"] for c in cfgs)  # 256 tiles do not fill whole waves of 148
@@ -22,6 +22,7 @@ def test_small_m_candidates_include_swap_and_split():
     args = T.TuneArgs("bf16", 32, 384, 7168, "nt", enable_split_k=True)
     cfgs = T.candidate_configs(args)
     assert any(c["swap_ab"] and c["tile_n"] == 32 and c["split_k"] >= 8 for c in cfgs)
+    assert any(c["split_mode"] == "cluster" and c["split_k"] == 16 for c in cfgs)
     # an N-contiguous operand on the tile_n axis cannot use tiles narrower than 64
     assert all(c["tile_n"] >= 64 for c in T.candidate_configs(T.TuneArgs("bf16", 200, 384, 1024, "nn")) if not c["swap_ab"])
 
