@@ -146,14 +146,37 @@ def time_config(args: TuneArgs, cfg: dict, sets, iters: int = 30) -> float:
     for i in range(3):
         s = sets[i % len(sets)]
         gemm_a16w16(s[0], s[1], s[3], bias=s[2], user_kwargs=cfg, layout=args.layout)
+    # Device time per call from CUDA-graph replay (no host launch overhead, like the reference's profiler-based
+    # kernel times); plain stream loop if the capture fails.
+    side = torch.cuda.Stream()
+    graph = None
+    try:
+        with torch.cuda.stream(side):
+            for i in range(2):
+                s = sets[i % len(sets)]
+                gemm_a16w16(s[0], s[1], s[3], bias=s[2], user_kwargs=cfg, layout=args.layout, stream=side)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(iters):
+                    s = sets[i % len(sets)]
+                    gemm_a16w16(s[0], s[1], s[3], bias=s[2], user_kwargs=cfg, layout=args.layout, stream=side)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+    except Exception:
+        graph = None
     times = []
     for rep in range(3):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         e0.record()
-        for i in range(iters):
-            s = sets[i % len(sets)]
-            gemm_a16w16(s[0], s[1], s[3], bias=s[2], user_kwargs=cfg, layout=args.layout)
+        if graph is not None:
+            graph.replay()
+        else:
+            for i in range(iters):
+                s = sets[i % len(sets)]
+                gemm_a16w16(s[0], s[1], s[3], bias=s[2], user_kwargs=cfg, layout=args.layout)
         e1.record()
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1) / iters * 1e3)
