@@ -29,7 +29,8 @@ class Policy(C.Structure):
         ("split_mode", C.c_int32),
         ("max_ctas", C.c_int32),
         ("stream_k", C.c_int32),
-        ("reserved", C.c_int32 * 7),
+        ("no_pdl", C.c_int32),
+        ("reserved", C.c_int32 * 6),
     ]
 
 

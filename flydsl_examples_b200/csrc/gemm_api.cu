@@ -310,7 +310,7 @@ struct RepackJob {
 struct b200_gemm_handle {
   b200::GemmParams params;
   b200::KernelFn fn;
-  int grid, smem_bytes, device, cta_group, cluster_split;
+  int grid, smem_bytes, device, cta_group, cluster_split, pdl;
   int n_repack;
   b200::RepackJob repack[2];
   b200_gemm_plan plan;
@@ -421,6 +421,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   h->smem_bytes = pl.smem_bytes;
   h->cta_group = pl.cta_group;
   h->cluster_split = pl.cluster_split;
+  h->pdl = a->policy.no_pdl ? 0 : 1;
   if (pl.cluster_split > 8) {
     // clusters of 16 CTAs are outside the portable range: the kernel has to opt in
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(h->fn), cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
@@ -449,15 +450,23 @@ static int run(const b200_gemm_handle* h, cudaStream_t stream) {
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = h->smem_bytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
   if (h->cta_group == 2 || h->cluster_split > 1) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = h->cta_group == 2 ? 2 : h->cluster_split;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = h->cta_group == 2 ? 2 : h->cluster_split;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
   }
+  if (h->pdl) {
+    // the kernel's set-up phase may overlap the previous kernel of this stream; it waits before touching memory
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  cfg.attrs = n_attr ? attr : nullptr;
+  cfg.numAttrs = n_attr;
   cudaError_t e = cudaLaunchKernelEx(&cfg, h->fn, h->params);
   if (e != cudaSuccess) return set_cuda_error(e);
   return 0;

@@ -321,6 +321,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
   }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_s;
+  // Everything above touched only this CTA's own shared memory, TMEM and kernel parameters, so with a programmatic
+  // dependent launch it overlaps the tail of the previous kernel in the stream. From here on global memory is read
+  // and written (operands may be that kernel's output; the workspace is shared with it).
+  grid_dependency_wait();
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (one per CTA)

@@ -218,6 +218,12 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[32])
       : "memory");
 }
 
+// Programmatic dependent launch: a grid launched with the stream-serialisation attribute may start while the grid
+// before it in the stream still runs; grid_dependency_wait() returns once that grid has completed and its writes
+// are visible (at once when there is no such dependency). grid_launch_dependents() lets the next grid start early.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

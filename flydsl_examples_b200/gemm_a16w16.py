@@ -148,11 +148,13 @@ def _strict_k_checks(k: int, kwargs: dict) -> None:
 
 def resolve_policy(m: int, n: int, k: int, dtype: torch.dtype, layout: str, user_kwargs: dict,
                    num_sms: int = _policy.NUM_SMS_DEFAULT) -> _policy.Policy:
-    """user_kwargs -> Policy. An empty dict first consults the tuned JSONL, then the heuristic."""
-    if not user_kwargs:
+    """user_kwargs -> Policy. A dict that names no tiling (empty, or control keys only) first consults the tuned
+    JSONL, then the heuristic."""
+    if not any(key in user_kwargs for key in _policy.REFERENCE_KEYS + _policy.BLACKWELL_KEYS):
         rec = _policy.tuned_lookup(_dtype_name(dtype), layout, m, n, k)
         if rec is not None:
-            return _policy.from_user_kwargs(rec, m, n, k, layout, num_sms)
+            control = {key: val for key, val in user_kwargs.items() if key in _policy.CONTROL_KEYS}
+            return _policy.from_user_kwargs({**rec, **control}, m, n, k, layout, num_sms)
     return _policy.from_user_kwargs(user_kwargs, m, n, k, layout, num_sms)
 
 
@@ -213,6 +215,7 @@ def _fill_args(a, b, out, bias, pol: _policy.Policy, a_t: bool, b_t: bool) -> _l
     p.split_mode = _policy.SPLIT_MODES[pol.split_mode]
     p.max_ctas = pol.max_ctas
     p.stream_k = 1 if pol.stream_k else 0
+    p.no_pdl = 0 if pol.pdl else 1
     return args
 
 

@@ -30,7 +30,8 @@ REFERENCE_KEYS = (
 )
 # Keys that only exist here.
 BLACKWELL_KEYS = ("tile_n", "swap_ab", "cta_group", "split_mode", "max_ctas", "stream_k")
-CONTROL_KEYS = ("strict_reference_envelope",)
+# Keys that switch behaviour without describing a tiling (they do not make a dict a "Blackwell policy").
+CONTROL_KEYS = ("strict_reference_envelope", "pdl")
 SPLIT_MODES = {"ticket": 0, "cluster": 2}
 
 
@@ -45,6 +46,7 @@ class Policy:
     split_mode: str = "ticket"
     max_ctas: int = 0
     stream_k: bool = False
+    pdl: bool = True         # programmatic dependent launch: set-up overlaps the previous kernel in the stream
 
     def as_dict(self) -> dict:
         return asdict(self)
@@ -245,8 +247,11 @@ def from_user_kwargs(user_kwargs: dict, m: int, n: int, k: int, layout: str, num
             fields["split_k"] = int(user_kwargs["split_k"])
         if "group_m" in user_kwargs:
             fields["group_m"] = int(user_kwargs["group_m"])
+    if "pdl" in user_kwargs:
+        fields["pdl"] = user_kwargs["pdl"]
     fields["swap_ab"] = bool(fields["swap_ab"])
     fields["stream_k"] = bool(fields["stream_k"])
+    fields["pdl"] = bool(fields["pdl"])
     pol = Policy(**fields)
     return pol
 
@@ -280,6 +285,11 @@ def load_tuned(path: Optional[Path] = None) -> dict[tuple, dict]:
 
 
 def tuned_lookup(dtype: str, layout: str, m: int, n: int, k: int) -> Optional[dict]:
+    """Tuned policy for this exact problem, if the table has one. fp16 and bf16 run the same kernels at the same
+    speed, so a row tuned for one serves the other."""
     if not _TUNED_LOADED:
         load_tuned()
-    return _TUNED.get((dtype, layout, m, n, k))
+    rec = _TUNED.get((dtype, layout, m, n, k))
+    if rec is None:
+        rec = _TUNED.get(("fp16" if dtype == "bf16" else "bf16", layout, m, n, k))
+    return rec

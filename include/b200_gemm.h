@@ -55,7 +55,10 @@ typedef struct b200_gemm_policy {
   int32_t split_mode; /* B200_GEMM_SPLIT_*                                                                       */
   int32_t max_ctas;   /* persistent grid size cap; 0 = number of SMs                                              */
   int32_t stream_k;   /* 1: tail-wave tiles are cut into K spans so every SM gets equal work                      */
-  int32_t reserved[7];
+  int32_t no_pdl;     /* 1: launch without programmatic dependent launch. By default the kernel's set-up (barriers,
+                         TMEM, descriptor prefetch) may overlap the end of the previous kernel in the stream; it
+                         waits for that kernel to complete before it reads or writes global memory               */
+  int32_t reserved[6];
 } b200_gemm_policy;
 
 /* One GEMM call. Replaces the argument list of the reference's jit host stub gemm_a16w16_gfx950

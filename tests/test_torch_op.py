@@ -1,0 +1,56 @@
+"""The torch.library registration: schema and shape inference on CPU (fake tensors), real call on the GPU."""
+import pytest
+import torch
+
+import flydsl_examples_b200.torch_op  # noqa: F401  (registers the operator)
+
+
+def test_operator_is_registered_with_a_schema():
+    op = torch.ops.b200.gemm_a16w16
+    schema = str(op.default._schema)
+    assert "Tensor a" in schema and "Tensor b" in schema and "Tensor? bias" in schema and "str layout" in schema
+
+
+def test_fake_tensor_shape_and_dtype_inference():
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        a = torch.empty(32, 7168, dtype=torch.bfloat16)
+        b = torch.empty(384, 7168, dtype=torch.bfloat16).t()
+        y = torch.ops.b200.gemm_a16w16(a, b, None, "nt", "fp32")
+        assert y.shape == (32, 384) and y.dtype is torch.float32
+        y = torch.ops.b200.gemm_a16w16(a, b, None, "nt", None)
+        assert y.dtype is torch.bfloat16
+        with pytest.raises(Exception):
+            torch.ops.b200.gemm_a16w16(a, torch.empty(5, 5, dtype=torch.bfloat16), None, "nn", None)
+
+
+@pytest.mark.gpu
+def test_operator_runs_and_matches_the_oracle():
+    from flydsl_examples_b200.gemm_a16w16 import check_status
+    from oracle import oracle as O
+
+    case = O.Case("op", "bf16", "nt", 96, 200, 512, seed=71, bias_std=0.5)
+    a, b, bias, a_l, b_l, bias_l = O.build_inputs(case, device="cuda")
+    y = torch.ops.b200.gemm_a16w16(a, b, bias, "nt", None)
+    check_status()
+    O.assert_close(y, O.reference_matmul(a_l, b_l, bias_l, torch.bfloat16), case.k, "custom op")
+    y32 = torch.ops.b200.gemm_a16w16(a, b, None, "nt", "fp32")
+    O.assert_close(y32, O.reference_matmul(a_l, b_l, None, torch.float32), case.k, "custom op fp32")
+
+
+@pytest.mark.gpu
+def test_operator_inside_torch_compile():
+    from flydsl_examples_b200.gemm_a16w16 import check_status
+    from oracle import oracle as O
+
+    case = O.Case("op_compile", "fp16", "nt", 64, 128, 256, seed=72)
+    a, b, _, a_l, b_l, _ = O.build_inputs(case, device="cuda")
+
+    @torch.compile(fullgraph=True, backend="eager")
+    def f(x, w):
+        return torch.ops.b200.gemm_a16w16(x, w, None, "nt", "fp32") * 2.0
+
+    y = f(a, b)
+    check_status()
+    O.assert_close(y, O.reference_matmul(a_l, b_l, None, torch.float32) * 2.0, case.k, "compiled")
