@@ -498,6 +498,24 @@ def run_ours(args) -> dict:
     }
     result.update(w.extra)
 
+    if world > 1 and workload == "c5_nshard":
+        # The same GEMM, whole, on one GPU (rank 0; the other ranks idle at the barrier): the denominator for scaling
+        # efficiency of this workload, measured in the same run under the same conditions.
+        single = None
+        if rank == 0:
+            del w
+            torch.cuda.empty_cache()
+            w1 = Workload("c5", args, 1, 0, device)
+            w1.step()
+            for _ in range(2):
+                w1.step()
+            ms1 = timed(stream, device, w1.step, max(3, min(args.steps, 10)), 1)
+            check_status(device)
+            single = {"value": w1.total_flops / (ms1 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms1,
+                      "workload": "c5: the whole GEMM on one GPU (rank 0), timed after the sharded run"}
+            result["single_gpu_same_workload"] = single
+            result["scaling_efficiency_vs_single_gpu"] = value / (world * single["value"])
+        dist.barrier()
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_reference_run(case)
         result["cpu_baseline"] = {"value": cpu["tflops"], "unit": "TFLOP/s", "cores": cpu["cores"], "kind": "port",
