@@ -443,6 +443,8 @@ static int run(const b200_gemm_handle* h, cudaStream_t stream) {
   for (int i = 0; i < h->n_repack; ++i) {
     const RepackJob& j = h->repack[i];
     repack_rows_kernel<<<j.blocks, 256, 0, stream>>>(j.src, j.src_ld, j.dst, j.dst_ld, j.rows, j.cols);
+    cudaError_t re = cudaGetLastError();
+    if (re != cudaSuccess) return set_cuda_error(re);
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));

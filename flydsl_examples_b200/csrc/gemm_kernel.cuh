@@ -315,9 +315,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
   tc_fence_before();
   __syncthreads();
   const bool cluster_mode = CG == 1 && p.cluster_split > 1;
-  if (CG == 2 || cluster_mode) {  // every CTA of the cluster is running before anything is sent across it
+  // Every CTA of a cluster must be running before anything is sent across it. A pair needs that before its first
+  // load (the peer's barriers are signalled from the start); cluster split-K only before the epilogue's scatter, so
+  // there each thread arrives now and waits later (`cluster_wait_due`), keeping the barrier off the load path.
+  bool cluster_wait_due = false;
+  if (CG == 2) {
     cluster_arrive();
     cluster_wait();
+  } else if (cluster_mode) {
+    cluster_arrive();
+    cluster_wait_due = true;
   }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_s;
@@ -583,6 +590,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       };
       uint32_t cl_dst = 0;
       if (cluster_mode) {
+        if (cluster_wait_due) {
+          cluster_wait();
+          cluster_wait_due = false;
+        }
         const int rows_per_cta = kTileP / p.cluster_split;
         const uint32_t local = base + L::kOutOff +
                                (uint32_t)(((int)cluster_ctarank() * rows_per_cta + row % rows_per_cta) * TILE_Q) * 4u;
@@ -700,11 +711,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       if (et == 0) trace_stamp(p, 2, it, 1);
       if (!direct && !cluster_mode) {
         // Ticket: the CTA that arrives last at this (half-)tile sums all contributions in slot order.
-        __threadfence();
+        // One thread fences for the group: the barrier orders every epilogue thread's partial stores before its
+        // fence (release, cumulative), and its second fence (acquire) plus the barrier orders the reads after.
         named_bar_sync(2, kEpiThreads);
         if (et == 0) {
           int* ticket = p.tickets + (w.tile * CG + rank);
+          __threadfence();
           const int t = atomicAdd(ticket, 1);
+          __threadfence();
           const int last = (t == w.n_contrib - 1) ? 1 : 0;
           if (last) *ticket = 0;  // self-cleaning: nobody else touches it until the next launch
           *last_s = last;
@@ -712,7 +726,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         named_bar_sync(2, kEpiThreads);
         const int last = *last_s;
         if (last) {
-          __threadfence();
           const float4* tp0 = reinterpret_cast<const float4*>(p.partials) + (size_t)(w.slot0 * CG + rank) * kSlotVec + row;
           constexpr int kBatch = 4;  // contributors whose loads are in flight together
 #pragma unroll 1
@@ -757,6 +770,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
   // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if (cluster_wait_due) cluster_wait();  // warps that did not take part in the scatter still owe the first wait
   if (CG == 2 || cluster_mode) {
     // pair: no CTA leaves while its peer may still signal it or use its TMEM half;
     // cluster split-K: every CTA's rows have arrived in their owner's shared memory

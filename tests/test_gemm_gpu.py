@@ -152,6 +152,23 @@ def test_config5_large_bf16_sampled_and_consistent():
     O.assert_close(got, lib, case.k, "c5 vs torch.matmul (secondary)")
 
 
+def test_golden_fixtures_through_the_cuda_path(golden):
+    # the committed vectors come from the reference's own ref_func (tests/golden/make_golden.py)
+    for name in (str(n) for n in golden["names"]):
+        dt, layout, fp32 = (str(x) for x in golden[f"{name}.meta"])
+        dtype = DT[dt]
+        a_l = torch.from_numpy(golden[f"{name}.a"].copy()).view(dtype)
+        b_l = torch.from_numpy(golden[f"{name}.b"].copy()).view(dtype)
+        bias_l = torch.from_numpy(golden[f"{name}.bias"].copy()).view(dtype) if f"{name}.bias" in golden.files else None
+        want = torch.from_numpy(golden[f"{name}.c"].copy())
+        want = want if fp32 == "1" else want.view(dtype)
+        a = O.place(a_l, layout[0] == "t", device=DEV)
+        b = O.place(b_l, layout[1] == "t", device=DEV)
+        got = gemm_a16w16(a, b, bias=None if bias_l is None else bias_l.to(DEV), layout=layout, out_dtype=want.dtype)
+        check_status()
+        O.assert_close(got, want, a_l.shape[1], f"golden {name}")
+
+
 # ------------------------------------------------------------------------------------------ reference case lists
 MAIN_LOOP = [  # (m, n, k, kw)  cf. test_gemm_a16w16_gfx950.py:262-283
     (1024, 1024, 1024, {"tile_n": 256}),
