@@ -223,7 +223,7 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
   // shared memory: no workspace, no tickets. One tile per cluster, so the grid is not persistent.
   pl.cluster_split = 0;
   if (pol.split_mode == B200_GEMM_SPLIT_CLUSTER && pl.split_k > 1 && !pl.stream_k) {
-    if (pl.cta_group != 1 || pl.tile_n > 64) return B200_GEMM_ERR_BAD_POLICY;
+    if (pl.cta_group != 1) return B200_GEMM_ERR_BAD_POLICY;
     int s = 16;
     while (s > pl.split_k) s >>= 1;  // largest power of two <= split_k (split_k was clamped to the K blocks)
     pl.split_k = s;

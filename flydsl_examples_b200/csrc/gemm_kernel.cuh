@@ -157,7 +157,10 @@ struct SmemLayout {
   // Epilogue staging for TMA stores: per epilogue warp two 32-row x 128-byte swizzled images (tiles >= 64 wide only).
   static constexpr int kStageOutBytes = 32 * 128;
   static constexpr int kOutOff = kRingBytes;
-  // The same region receives the other CTAs' rows in cluster split-K mode: float[S][128/S][TILE_Q] (TILE_Q <= 64).
+  // In cluster split-K mode the other CTAs' rows arrive in float[S][128/S][TILE_Q]: in this region for tiles up to 64
+  // wide; wider tiles reuse the operand ring instead (it is idle once the last MMA has completed).
+  static constexpr bool kRecvInRing = TILE_Q > 64;
+  static constexpr int kRecvOff = kRecvInRing ? 0 : kRingBytes;
   static constexpr int kRecvBytes = TILE_Q <= 64 ? kTileP * TILE_Q * 4 : 0;
   static constexpr int kStagingBytes = TILE_Q >= 64 ? 4 * 2 * kStageOutBytes : 0;
   static constexpr int kOutBytes = kRecvBytes > kStagingBytes ? kRecvBytes : kStagingBytes;
@@ -319,6 +322,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
   // load (the peer's barriers are signalled from the start); cluster split-K only before the epilogue's scatter, so
   // there each thread arrives now and waits later (`cluster_wait_due`), keeping the barrier off the load path.
   bool cluster_wait_due = false;
+  // Wide tiles receive into the operand ring, so every CTA of the cluster must have finished its MMAs before anyone
+  // scatters: one more cluster barrier ("ring idle"), owed by every thread exactly once.
+  bool ring_idle_barrier_due = cluster_mode && L::kRecvInRing;
   if (CG == 2) {
     cluster_arrive();
     cluster_wait();
@@ -588,16 +594,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
             mbar_arrive(acce_bar(buf));
         }
       };
-      uint32_t cl_dst = 0;
+      uint32_t cl_dst = 0, cl_swz = 0;
       if (cluster_mode) {
         if (cluster_wait_due) {
           cluster_wait();
           cluster_wait_due = false;
         }
+        if (ring_idle_barrier_due) {  // this CTA's accumulator is complete, so its ring is idle: tell the cluster
+          cluster_arrive();
+          cluster_wait();
+          ring_idle_barrier_due = false;
+        }
         const int rows_per_cta = kTileP / p.cluster_split;
-        const uint32_t local = base + L::kOutOff +
+        const uint32_t local = base + L::kRecvOff +
                                (uint32_t)(((int)cluster_ctarank() * rows_per_cta + row % rows_per_cta) * TILE_Q) * 4u;
         cl_dst = mapa_cluster(local, (uint32_t)(row / rows_per_cta));
+        cl_swz = (uint32_t)((row % rows_per_cta) & 7) & (uint32_t)(TILE_Q / 4 - 1);
       }
       // TMA-store path: bias + cast, then this lane's row segment goes into the warp's swizzled staging image
       // (16-byte chunk j of row t sits at position j ^ (t % 8)); every full 128-byte row image is stored by one lane.
@@ -671,12 +683,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         } else if (direct) {
           finalize_chunk<CW>(p, v, prow, qbase + c * CW, bias_s + c * CW, bias_p);
         } else if (cluster_mode) {
-          // cluster split-K: this row's partial sums go to the CTA that owns the row, into slab [my rank][row % R]
+          // cluster split-K: this row's partial sums go to the CTA that owns the row, into slab [my rank][row % R].
+          // 16-byte chunk g of a row is stored at position g ^ (row % 8) (capped to the chunks a row has), so that the
+          // 32 lanes of a warp, which write 32 different rows, spread over all banks of the receiver.
 #pragma unroll
-          for (int j = 0; j < CW / 4; ++j)
-            asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cl_dst + (uint32_t)(c * CW + 4 * j) * 4u), "f"(v[4 * j]),
-                         "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+          for (int j = 0; j < CW / 4; ++j) {
+            const uint32_t g = (uint32_t)(c * (CW / 4) + j) ^ cl_swz;
+            asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cl_dst + g * 16u), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                         "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
                          : "memory");
+          }
         } else {
           // slot layout [chunk][4-column group][row][4]: one warp store covers 512 contiguous bytes
           float4* dst = part + (size_t)c * (CW / 4) * kTileP;
@@ -768,33 +784,32 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
   }
 
   // ---------------------------------------------------------------------- teardown
+  // Cluster barriers that this thread still owes come BEFORE the CTA-wide barrier: the epilogue warps pass them inside
+  // their loop, so a producer / MMA warp that first waited for them at __syncthreads would never arrive (deadlock).
+  if (cluster_wait_due) cluster_wait();  // warps that did not take part in the scatter still owe the first wait
+  if (ring_idle_barrier_due) {           // ... and the "ring idle" barrier
+    cluster_arrive();
+    cluster_wait();
+  }
   tc_fence_before();
   __syncthreads();
-  if (cluster_wait_due) cluster_wait();  // warps that did not take part in the scatter still owe the first wait
   if (CG == 2 || cluster_mode) {
     // pair: no CTA leaves while its peer may still signal it or use its TMEM half;
     // cluster split-K: every CTA's rows have arrived in their owner's shared memory
     cluster_arrive();
     cluster_wait();
   }
-  if constexpr (CG == 1 && TILE_Q <= 64) {
+  if constexpr (CG == 1) {
     if (cluster_mode && warp >= 2) {
-      // Each CTA owns 128/S rows of the tile: sum the S slabs in rank order (deterministic), bias, cast, store.
+      // Each CTA owns R = 128/S rows of the tile: sum the S slabs in rank order (deterministic), bias, cast, store.
       const int S = p.cluster_split, R = kTileP / S;
       const int crank = (int)cluster_ctarank();
       const int tile = (int)blockIdx.x / S;
       int tp, tq;
       raster_tile(p, tile, tp, tq);
-      const float* recv = reinterpret_cast<const float*>(sm + L::kOutOff);
+      const float* recv = reinterpret_cast<const float*>(sm + L::kRecvOff);
       const int et = threadIdx.x - 64;
-      for (int e = et; e < R * TILE_Q; e += kEpiThreads) {
-        // D^T output: consecutive threads take consecutive rows (contiguous in memory); else consecutive columns
-        const int lrow = p.swap_out ? e % R : e / TILE_Q;
-        const int col = p.swap_out ? e / R : e % TILE_Q;
-        float acc = 0.f;
-        for (int src = 0; src < S; ++src) acc += recv[(src * R + lrow) * TILE_Q + col];
-        const int prow = tp * kTileP + crank * R + lrow;
-        const int q = tq * TILE_Q + col;
+      auto emit = [&](float acc, int prow, int q) {
         if (prow < p.P && q < p.Q) {
           if (p.bias != nullptr) acc += load_in_as_float(p.bias, p.swap_out ? prow : q, p.in_dtype);
           const long long idx = p.swap_out ? (long long)q * p.ldo + prow : (long long)prow * p.ldo + q;
@@ -804,6 +819,60 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
             reinterpret_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(acc);
           else
             reinterpret_cast<__half*>(p.out)[idx] = __float2half_rn(acc);
+        }
+      };
+      constexpr uint32_t kSwzMask = TILE_Q / 4 - 1;  // TILE_Q / 4 chunks per row (a power of two)
+      if (!p.swap_out) {
+        // four consecutive columns per thread and step: float4 reads of the slabs, bias from the staged slice,
+        // one 8- or 16-byte store (scalar stores at ragged edges or unaligned rows)
+        const int es = p.out_dtype == 1 ? 4 : 2;
+#pragma unroll 2
+        for (int e = et; e < R * (TILE_Q / 4); e += kEpiThreads) {
+          const int lrow = e / (TILE_Q / 4), g = e % (TILE_Q / 4), col = g * 4;
+          const int gs = (int)((uint32_t)g ^ ((uint32_t)(lrow & 7) & kSwzMask));
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int src = 0; src < S; ++src) {
+            const float4 x = *reinterpret_cast<const float4*>(recv + (src * R + lrow) * TILE_Q + gs * 4);
+            acc.x += x.x, acc.y += x.y, acc.z += x.z, acc.w += x.w;
+          }
+          const int prow = tp * kTileP + crank * R + lrow, q = tq * TILE_Q + col;
+          if (prow >= p.P || q >= p.Q) continue;
+          if (p.bias != nullptr) acc.x += bias_s[col], acc.y += bias_s[col + 1], acc.z += bias_s[col + 2], acc.w += bias_s[col + 3];
+          char* dst = reinterpret_cast<char*>(p.out) + ((long long)prow * p.ldo + q) * es;
+          if (q + 3 < p.Q && (reinterpret_cast<uintptr_t>(dst) & (uintptr_t)(4 * es - 1)) == 0) {
+            if (p.out_dtype == 1) {
+              *reinterpret_cast<float4*>(dst) = acc;
+            } else if (p.out_dtype == 2) {
+              __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+              *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            } else {
+              __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+              *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            }
+          } else {
+            const float a4[4] = {acc.x, acc.y, acc.z, acc.w};
+            for (int t = 0; t < 4; ++t) {
+              if (q + t < p.Q) {
+                const long long idx = (long long)prow * p.ldo + q + t;
+                if (p.out_dtype == 1)
+                  reinterpret_cast<float*>(p.out)[idx] = a4[t];
+                else if (p.out_dtype == 2)
+                  reinterpret_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(a4[t]);
+                else
+                  reinterpret_cast<__half*>(p.out)[idx] = __float2half_rn(a4[t]);
+              }
+            }
+          }
+        }
+      } else {
+        // D^T output: consecutive threads take consecutive rows, which are contiguous in memory
+#pragma unroll 4
+        for (int e = et; e < R * TILE_Q; e += kEpiThreads) {
+          const int lrow = e % R, col = e / R;
+          const int off = (int)((((uint32_t)(col >> 2)) ^ ((uint32_t)(lrow & 7) & kSwzMask)) * 4u) + (col & 3);
+          float acc = 0.f;
+          for (int src = 0; src < S; ++src) acc += recv[(src * R + lrow) * TILE_Q + off];
+          emit(acc, tp * kTileP + crank * R + lrow, tq * TILE_Q + col);
         }
       }
     }

@@ -148,8 +148,8 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
         return f"split_mode must be one of {tuple(SPLIT_MODES)}, got {pol.split_mode!r}"
     if pol.group_m < 0:
         return f"group_m must be >= 0, got {pol.group_m}"
-    if pol.split_mode == "cluster" and pol.split_k > 1 and (pol.cta_group != 1 or pol.tile_n > 64 or pol.stream_k):
-        return "cluster split-K needs cta_group 1, tile_n <= 64 and no stream_k"
+    if pol.split_mode == "cluster" and pol.split_k > 1 and (pol.cta_group != 1 or pol.stream_k):
+        return "cluster split-K needs cta_group 1 and no stream_k"
     # The operand on the MMA N axis, when it is contiguous along N (or M after a swap), is fetched as 64-wide boxes.
     a_mn = layout[0] == "t"
     b_mn = layout[1] == "n"
@@ -186,7 +186,7 @@ def _auto_split(tiles: int, kb: int, walkers: int, cluster_ok: bool = False) -> 
 def _estimate_cycles(p_ext: int, q: int, kb: int, cta_group: int, tile_n: int, num_sms: int) -> float:
     walkers = max(1, num_sms // cta_group)
     tiles = -(-p_ext // (TILE_M * cta_group)) * -(-q // tile_n)
-    split, _ = _auto_split(tiles, kb, walkers, cta_group == 1 and tile_n <= 64)
+    split, _ = _auto_split(tiles, kb, walkers, cta_group == 1)
     waves = -(-(tiles * split) // walkers)
     epilogue = 1000.0 + 500.0 * tile_n / 256
     fixup = (1500.0 + 400.0 * split) if split > 1 else 0.0
@@ -215,7 +215,7 @@ def heuristic(m: int, n: int, k: int, layout: str = "nt", num_sms: int = NUM_SMS
         cta_group, tile_n = best
     walkers = num_sms // cta_group
     tiles = -(-p_ext // (TILE_M * cta_group)) * -(-q // tile_n)
-    split, mode = _auto_split(tiles, kb, walkers, cta_group == 1 and tile_n <= 64)
+    split, mode = _auto_split(tiles, kb, walkers, cta_group == 1)
     group = 8 if (tiles >= 2 * walkers and not swap) else 0
     return Policy(tile_n=tile_n, split_k=split, group_m=group, swap_ab=swap, cta_group=cta_group, split_mode=mode)
 

@@ -65,7 +65,7 @@ def candidate_configs(args: TuneArgs, num_sms: int = P.NUM_SMS_DEFAULT) -> list[
             for s in (2, 3, 4, 6, 8, 12, 16, 24, 32, 48):
                 if s <= kb and tiles * s <= 4 * walkers:
                     splits.append((s, False, "ticket"))
-            if cg == 1 and tile_n <= 64:
+            if cg == 1:
                 for s in (2, 4, 8, 16):  # K slices as one thread-block cluster
                     if s <= kb and tiles * s <= 2 * walkers:
                         splits.append((s, False, "cluster"))

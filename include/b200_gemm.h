@@ -40,8 +40,9 @@ extern "C" {
 #define B200_GEMM_SPLIT_ATOMIC 1  /* reserved                                                                      */
 #define B200_GEMM_SPLIT_CLUSTER 2 /* the K slices of a tile are the CTAs of one thread-block cluster (2, 4, 8 or 16);
                                      each CTA sends its partial rows to the row's owner through distributed shared
-                                     memory, one cluster barrier, owners sum in rank order. No workspace, no tickets,
-                                     deterministic. tile_n <= 64, cta_group 1; split_k is rounded down to a power of two */
+                                     memory, a cluster barrier, owners sum in rank order. No workspace, no tickets,
+                                     deterministic. cta_group 1; split_k is rounded down to a power of two. Tiles wider
+                                     than 64 receive into the idle operand ring (one more cluster barrier)          */
 
 /* Blackwell policy. Replaces the reference's compile-time GemmA16W16Gfx950Param
  * (kernels/gemm_a16w16_gfx950.py:33-61): block_m/n/k, stages, split_k, *_waves, group_m, HTI flag. */

@@ -85,6 +85,10 @@ CLUSTER_SPLIT = [
     (129, 136, 1536, {"tile_n": 64, "split_k": 16, "split_mode": "cluster"}),
     (48, 5120, 2880, {"tile_n": 64, "swap_ab": True, "split_k": 2, "split_mode": "cluster"}),
     (200, 328, 333, {"tile_n": 32, "split_k": 16, "split_mode": "cluster"}),   # 6 K blocks: rounds down to 4 slices
+    (256, 4096, 4096, {"tile_n": 128, "split_k": 2, "split_mode": "cluster"}),  # wide tiles receive into the idle ring
+    (300, 700, 2048, {"tile_n": 256, "split_k": 8, "split_mode": "cluster"}),
+    (800, 384, 7168, {"tile_n": 128, "split_k": 4, "split_mode": "cluster"}),
+    (100, 600, 1000, {"tile_n": 128, "swap_ab": True, "split_k": 4, "split_mode": "cluster"}),
 ]
 
 
