@@ -30,7 +30,8 @@ class Policy(C.Structure):
         ("max_ctas", C.c_int32),
         ("stream_k", C.c_int32),
         ("no_pdl", C.c_int32),
-        ("reserved", C.c_int32 * 6),
+        ("tile_k", C.c_int32),
+        ("reserved", C.c_int32 * 5),
     ]
 
 
@@ -91,6 +92,17 @@ class Plan(C.Structure):
         return {name: getattr(self, name) for name, _ in self._fields_}
 
 
+class PeerHandle(C.Structure):
+    """b200_peer_handle: plain bytes, safe to pickle with bytes(handle) and rebuild with from_buffer_copy."""
+    _fields_ = [
+        ("ipc", C.c_uint8 * 64),
+        ("offset", C.c_uint64),
+        ("bytes", C.c_uint64),
+        ("device", C.c_int32),
+        ("reserved", C.c_int32),
+    ]
+
+
 EXPORTS = (
     "b200_gemm_a16w16",
     "b200_gemm_a16w16_static_scratch",
@@ -102,6 +114,10 @@ EXPORTS = (
     "b200_gemm_num_variants",
     "b200_gemm_describe_variant",
     "b200_gemm_cast_bias",
+    "b200_gemm_reduce_slots",
+    "b200_peer_export",
+    "b200_peer_open",
+    "b200_peer_close",
     "b200_gemm_strerror",
     "b200_gemm_version",
 )
@@ -147,10 +163,20 @@ def load() -> C.CDLL:
     lib.b200_gemm_workspace_bytes.restype = C.c_uint64
     lib.b200_gemm_num_variants.argtypes = []
     lib.b200_gemm_num_variants.restype = C.c_int
-    lib.b200_gemm_describe_variant.argtypes = [C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
+    lib.b200_gemm_describe_variant.argtypes = [C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                               C.POINTER(C.c_int32)]
     lib.b200_gemm_describe_variant.restype = C.c_int
     lib.b200_gemm_cast_bias.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]
     lib.b200_gemm_cast_bias.restype = C.c_int
+    lib.b200_gemm_reduce_slots.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                           C.c_int32, C.c_int32, C.c_void_p]
+    lib.b200_gemm_reduce_slots.restype = C.c_int
+    lib.b200_peer_export.argtypes = [C.c_void_p, C.POINTER(PeerHandle)]
+    lib.b200_peer_export.restype = C.c_int
+    lib.b200_peer_open.argtypes = [C.POINTER(PeerHandle), C.POINTER(C.c_void_p)]
+    lib.b200_peer_open.restype = C.c_int
+    lib.b200_peer_close.argtypes = [C.c_void_p, C.POINTER(PeerHandle)]
+    lib.b200_peer_close.restype = C.c_int
     lib.b200_gemm_strerror.argtypes = [C.c_int]
     lib.b200_gemm_strerror.restype = C.c_char_p
     lib.b200_gemm_version.argtypes = []
@@ -170,7 +196,7 @@ def variants() -> list[dict]:
     lib = load()
     out = []
     for i in range(lib.b200_gemm_num_variants()):
-        tn, cg, ms = C.c_int32(), C.c_int32(), C.c_int32()
-        lib.b200_gemm_describe_variant(i, C.byref(tn), C.byref(cg), C.byref(ms))
-        out.append({"tile_n": tn.value, "cta_group": cg.value, "max_stages": ms.value})
+        tn, cg, ms, tk = C.c_int32(), C.c_int32(), C.c_int32(), C.c_int32()
+        lib.b200_gemm_describe_variant(i, C.byref(tn), C.byref(cg), C.byref(ms), C.byref(tk))
+        out.append({"tile_n": tn.value, "cta_group": cg.value, "max_stages": ms.value, "tile_k": tk.value})
     return out

@@ -35,48 +35,75 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+typedef CUresult (*GetAddressRangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+
+static GetAddressRangeFn get_address_range_fn() {
+  static GetAddressRangeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<GetAddressRangeFn>(ptr);
+  });
+  return fn;
+}
+
 static thread_local char g_last_cuda_error[256] = "";
 
 // ------------------------------------------------------------------ variant table
 typedef void (*KernelFn)(const GemmParams);
 struct Variant {
-  int tile_q, cta_group, max_stages;
+  int tile_q, cta_group, tile_k, max_stages;
   KernelFn fn[13];  // indexed by stage count (2..12)
 };
 
-template <int TILE_Q, int S, int CG>
+template <int TILE_Q, int S, int CG, int TK>
 constexpr KernelFn kfn() {
-  if constexpr (SmemLayout<TILE_Q, S, CG>::kDynBytes <= kSmemLimit)
-    return gemm_a16w16_sm100_kernel<TILE_Q, S, CG>;
+  if constexpr (SmemLayout<TILE_Q, S, CG, TK>::kDynBytes <= kSmemLimit)
+    return gemm_a16w16_sm100_kernel<TILE_Q, S, CG, TK>;
   else
     return nullptr;
 }
 
-#define B200_VARIANT(TQ, CG, MAXS)                                                                                \
+// Stages of 64 K elements: wide tiles and CTA pairs. Stages of 128 K elements: narrow single-CTA tiles.
+#define B200_VARIANT_K64(TQ, CG, MAXS)                                                                            \
   {                                                                                                               \
-    TQ, CG, MAXS, {                                                                                               \
-      nullptr, nullptr, kfn<TQ, 2, CG>(), kfn<TQ, 3, CG>(), kfn<TQ, 4, CG>(), kfn<TQ, 5, CG>(), kfn<TQ, 6, CG>(), \
-          nullptr, kfn<TQ, 8, CG>(), nullptr, kfn<TQ, 10, CG>(), nullptr, nullptr                                 \
+    TQ, CG, 64, MAXS, {                                                                                           \
+      nullptr, nullptr, kfn<TQ, 2, CG, 64>(), kfn<TQ, 3, CG, 64>(), kfn<TQ, 4, CG, 64>(), kfn<TQ, 5, CG, 64>(),   \
+          kfn<TQ, 6, CG, 64>(), nullptr, kfn<TQ, 8, CG, 64>(), nullptr, nullptr, nullptr, nullptr                 \
+    }                                                                                                             \
+  }
+#define B200_VARIANT_K128(TQ, MAXS)                                                                               \
+  {                                                                                                               \
+    TQ, 1, 128, MAXS, {                                                                                           \
+      nullptr, nullptr, kfn<TQ, 2, 1, 128>(), kfn<TQ, 3, 1, 128>(), kfn<TQ, 4, 1, 128>(), kfn<TQ, 5, 1, 128>(),   \
+          nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr                                           \
     }                                                                                                             \
   }
 
 static const Variant kVariants[] = {
-    B200_VARIANT(16, 1, 10), B200_VARIANT(32, 1, 10), B200_VARIANT(64, 1, 8), B200_VARIANT(128, 1, 6),
-    B200_VARIANT(256, 1, 4), B200_VARIANT(128, 2, 8), B200_VARIANT(256, 2, 6),
+    // The first entry of a (tile, cta_group) is the default when the policy leaves tile_k at 0.
+    B200_VARIANT_K128(16, 5),     B200_VARIANT_K128(32, 5),    B200_VARIANT_K128(64, 4),    B200_VARIANT_K128(128, 3),
+    B200_VARIANT_K64(256, 1, 4),  B200_VARIANT_K64(128, 2, 8), B200_VARIANT_K64(256, 2, 6),
+    B200_VARIANT_K64(16, 1, 8),   B200_VARIANT_K64(32, 1, 8),  B200_VARIANT_K64(64, 1, 8),  B200_VARIANT_K64(128, 1, 6),
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
-static const Variant* find_variant(int tile_q, int cta_group) {
+static const Variant* find_variant(int tile_q, int cta_group, int tile_k) {
   for (int i = 0; i < kNumVariants; ++i)
-    if (kVariants[i].tile_q == tile_q && kVariants[i].cta_group == cta_group) return &kVariants[i];
+    if (kVariants[i].tile_q == tile_q && kVariants[i].cta_group == cta_group &&
+        (tile_k == 0 || kVariants[i].tile_k == tile_k))
+      return &kVariants[i];
   return nullptr;
 }
 
-static int dyn_smem_bytes(int tile_q, int stages, int cta_group) {
+static int dyn_smem_bytes(int tile_q, int stages, int cta_group, int tile_k) {
   const int staging0 = tile_q >= 64 ? 4 * 2 * 32 * 128 : 0;
   const int recv = tile_q <= 64 ? kTileP * tile_q * 4 : 0;
   const int staging = recv > staging0 ? recv : staging0;
-  return stages * (kUStageBytes + (tile_q / cta_group) * kTileK * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024;
+  return stages * (kTileP * tile_k * 2 + (tile_q / cta_group) * tile_k * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024;
 }
 
 struct DeviceInfo {
@@ -137,10 +164,10 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
   pl.swap_ab = pol.swap_ab ? 1 : 0;
   pl.tile_m = kTileP * pl.cta_group;
   pl.tile_n = pol.tile_n;
-  pl.tile_k = kTileK;
   pl.group_m = pol.group_m < 0 ? 0 : pol.group_m;
-  const Variant* var = find_variant(pl.tile_n, pl.cta_group);
+  const Variant* var = find_variant(pl.tile_n, pl.cta_group, pol.tile_k);
   if (var == nullptr) return B200_GEMM_ERR_BAD_POLICY;
+  pl.tile_k = var->tile_k;
 
   // A is K-major when 'n'; B[K,N] is K-major when 't'.
   const int a_mn = a->a_trans ? 1 : 0;
@@ -165,7 +192,7 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
   pl.tiles_p = (r->P + pl.tile_m - 1) / pl.tile_m;
   pl.tiles_q = (r->Q + pl.tile_n - 1) / pl.tile_n;
   const int64_t tiles = (int64_t)pl.tiles_p * pl.tiles_q;
-  const int kb_total = (int)((a->k + kTileK - 1) / kTileK);
+  const int kb_total = (int)((a->k + pl.tile_k - 1) / pl.tile_k);
   pl.split_k = pol.split_k <= 0 ? 1 : pol.split_k;
   if (pl.split_k > kb_total) pl.split_k = kb_total;  // never an empty slice
   if (tiles * pl.split_k > 0x7fffffffLL) return B200_GEMM_ERR_TOO_LARGE;
@@ -176,7 +203,7 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
   while (stages >= 2 && (var->fn[stages] == nullptr)) --stages;
   if (stages < 2) return B200_GEMM_ERR_BAD_POLICY;
   pl.stages = stages;
-  pl.smem_bytes = dyn_smem_bytes(pl.tile_n, stages, pl.cta_group);
+  pl.smem_bytes = dyn_smem_bytes(pl.tile_n, stages, pl.cta_group, pl.tile_k);
   pl.tmem_cols = 2 * pl.tile_n < 32 ? 32 : 2 * pl.tile_n;
 
   int sms = sm_count_hint;
@@ -261,10 +288,10 @@ static int encode_operand(CUtensorMap* map, const void* ptr, int in_dtype, int m
   cuuint32_t box[2], estr[2] = {1, 1};
   if (!mn_major) {
     dims[0] = (cuuint64_t)k, dims[1] = (cuuint64_t)rows;
-    box[0] = kTileK, box[1] = (cuuint32_t)box_rows;
+    box[0] = kBoxK, box[1] = (cuuint32_t)box_rows;
   } else {
     dims[0] = (cuuint64_t)rows, dims[1] = (cuuint64_t)k;
-    box[0] = 64, box[1] = kTileK;
+    box[0] = 64, box[1] = kBoxK;
   }
   strides[0] = (cuuint64_t)ld * 2;
   const CUresult res = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -399,7 +426,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   p.ldo = a->ldo;
   p.P = r.P, p.Q = r.Q, p.K = (int)a->k;
   p.tiles_p = pl.tiles_p, p.tiles_q = pl.tiles_q, p.num_tiles = pl.tiles_p * pl.tiles_q;
-  p.kb_total = (int)((a->k + kTileK - 1) / kTileK);
+  p.kb_total = (int)((a->k + pl.tile_k - 1) / pl.tile_k);
   p.split_k = pl.split_k;
   p.cluster_split = pl.cluster_split;
   p.num_units = pl.num_units;
@@ -414,7 +441,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   make_desc(r.u_mn, &p.u_desc_hi, &p.u_desc_lo, &p.u_kstep);
   make_desc(r.v_mn, &p.v_desc_hi, &p.v_desc_lo, &p.v_kstep);
 
-  const Variant* var = find_variant(pl.tile_n, pl.cta_group);
+  const Variant* var = find_variant(pl.tile_n, pl.cta_group, pl.tile_k);
   const int vi = (int)(var - kVariants);
   h->fn = var->fn[pl.stages];
   h->grid = pl.grid;
@@ -581,11 +608,12 @@ uint64_t b200_gemm_workspace_bytes(const b200_gemm_args* args) {
 
 int b200_gemm_num_variants(void) { return b200::kNumVariants; }
 
-int b200_gemm_describe_variant(int index, int32_t* tile_n, int32_t* cta_group, int32_t* max_stages) {
+int b200_gemm_describe_variant(int index, int32_t* tile_n, int32_t* cta_group, int32_t* max_stages, int32_t* tile_k) {
   if (index < 0 || index >= b200::kNumVariants) return B200_GEMM_ERR_BAD_ARG;
   if (tile_n) *tile_n = b200::kVariants[index].tile_q;
   if (cta_group) *cta_group = b200::kVariants[index].cta_group;
   if (max_stages) *max_stages = b200::kVariants[index].max_stages;
+  if (tile_k) *tile_k = b200::kVariants[index].tile_k;
   return 0;
 }
 
@@ -607,6 +635,65 @@ int b200_gemm_cast_bias(const float* in, void* out, const void* bias, int64_t ro
   return 0;
 }
 
+int b200_gemm_reduce_slots(const float* slots, int64_t slot_stride, int32_t n_slots, void* out, const void* bias,
+                           int64_t rows, int64_t cols, int32_t out_dtype, int32_t bias_dtype, void* cuda_stream) {
+  if (slots == nullptr || out == nullptr || n_slots < 1 || rows < 0 || cols <= 0 || cols > 0x7fffffffLL)
+    return B200_GEMM_ERR_BAD_ARG;
+  if (out_dtype < 1 || out_dtype > 3) return B200_GEMM_ERR_BAD_ARG;
+  if (bias != nullptr && bias_dtype != B200_GEMM_DTYPE_BF16 && bias_dtype != B200_GEMM_DTYPE_FP16) return B200_GEMM_ERR_BAD_ARG;
+  if (cols % 4 != 0 || slot_stride % 4 != 0 || (n_slots > 1 && slot_stride < rows * cols) ||
+      (reinterpret_cast<uintptr_t>(slots) & 15) != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0)
+    return B200_GEMM_ERR_BAD_ARG;
+  if (rows == 0) return 0;
+  const long long total4 = rows * cols / 4;
+  const long long want = (total4 + 255) / 256;
+  const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+  b200::reduce_slots_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(
+      slots, slot_stride, n_slots, out, bias, rows, (int)cols, out_dtype, bias_dtype);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return b200::set_cuda_error(e);
+  return 0;
+}
+
+int b200_peer_export(const void* ptr, b200_peer_handle* handle) {
+  if (ptr == nullptr || handle == nullptr) return B200_GEMM_ERR_BAD_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == sizeof(handle->ipc), "IPC handle size");
+  b200::GetAddressRangeFn range = b200::get_address_range_fn();
+  if (range == nullptr) return B200_GEMM_ERR_DRIVER;
+  CUdeviceptr base = 0;
+  size_t bytes = 0;
+  if (range(&base, &bytes, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS) return B200_GEMM_ERR_BAD_ARG;
+  memset(handle, 0, sizeof(*handle));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
+  if (e != cudaSuccess) return b200::set_cuda_error(e);
+  memcpy(handle->ipc, &h, sizeof(h));
+  handle->offset = reinterpret_cast<uintptr_t>(ptr) - (uintptr_t)base;
+  handle->bytes = bytes - handle->offset;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return B200_GEMM_ERR_LAUNCH;
+  handle->device = dev;
+  return 0;
+}
+
+int b200_peer_open(const b200_peer_handle* handle, void** ptr) {
+  if (handle == nullptr || ptr == nullptr) return B200_GEMM_ERR_BAD_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle->ipc, sizeof(h));
+  void* base = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return b200::set_cuda_error(e);
+  *ptr = static_cast<char*>(base) + handle->offset;
+  return 0;
+}
+
+int b200_peer_close(void* ptr, const b200_peer_handle* handle) {
+  if (ptr == nullptr || handle == nullptr) return B200_GEMM_ERR_BAD_ARG;
+  cudaError_t e = cudaIpcCloseMemHandle(static_cast<char*>(ptr) - handle->offset);
+  if (e != cudaSuccess) return b200::set_cuda_error(e);
+  return 0;
+}
+
 const char* b200_gemm_strerror(int code) {
   switch (code) {
     case B200_GEMM_OK: return "ok";
@@ -615,7 +702,7 @@ const char* b200_gemm_strerror(int code) {
     case B200_GEMM_ERR_WORKSPACE: return "workspace missing, misaligned (256 B) or smaller than b200_gemm_workspace_bytes()";
     case B200_GEMM_ERR_TENSOR_MAP: return "cuTensorMapEncodeTiled rejected an operand";
     case B200_GEMM_ERR_LAUNCH: return b200::g_last_cuda_error[0] ? b200::g_last_cuda_error : "CUDA runtime error";
-    case B200_GEMM_ERR_DRIVER: return "cuTensorMapEncodeTiled driver entry point not available";
+    case B200_GEMM_ERR_DRIVER: return "a CUDA driver entry point (cuTensorMapEncodeTiled, cuMemGetAddressRange) is not available";
     case B200_GEMM_ERR_TOO_LARGE: return "size beyond a fixed limit of this entry point";
     default: return "unknown error code";
   }

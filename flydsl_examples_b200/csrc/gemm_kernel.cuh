@@ -24,11 +24,11 @@
 namespace b200 {
 
 constexpr int kTileP = 128;  // rows of U per CTA tile (MMA M)
-constexpr int kTileK = 64;   // K elements per stage = one 128-byte swizzle span of 16-bit data
+constexpr int kBoxK = 64;    // K elements per TMA box = one 128-byte swizzle span of 16-bit data
 constexpr int kUmmaK = 16;   // K elements per tcgen05.mma kind::f16
 constexpr int kThreads = 192;
 constexpr int kEpiThreads = 128;
-constexpr int kUStageBytes = kTileP * kTileK * 2;  // 16 KB
+constexpr int kUBoxBytes = kTileP * kBoxK * 2;  // 16 KB: the 128 U rows of one 64-deep K box
 
 struct alignas(64) GemmParams {
   CUtensorMap tmap_u;
@@ -44,7 +44,7 @@ struct alignas(64) GemmParams {
   long long ldo;    // output row stride (elements)
   int P, Q, K;
   int tiles_p, tiles_q, num_tiles;
-  int kb_total;  // ceil(K / 64)
+  int kb_total;  // ceil(K / TK): K blocks of one pipeline stage each
   int split_k;
   int cluster_split;  // > 1: the split_k CTAs of a tile form one thread-block cluster and reduce through DSMEM
   int num_units;
@@ -148,10 +148,15 @@ struct WorkIter {
 
 // CG = CTAs that share one output tile: 1, or 2 for a tcgen05 cta_group::2 pair (each CTA then holds 128 of the
 // tile's 256 U rows and half of its V rows).
-template <int TILE_Q, int STAGES, int CG>
+// TK = K elements per pipeline stage: 64, or 128 (two boxes per operand) for narrow tiles, where the fixed cost of a
+// stage (barrier poll, election, commit) would otherwise exceed the few tensor cycles a 64-deep block needs.
+template <int TILE_Q, int STAGES, int CG, int TK>
 struct SmemLayout {
+  static constexpr int kSub = TK / kBoxK;  // 64-deep boxes per operand and stage
   static constexpr int kVRows = TILE_Q / CG;
-  static constexpr int kVStageBytes = kVRows * kTileK * 2;
+  static constexpr int kVBoxBytes = kVRows * kBoxK * 2;
+  static constexpr int kUStageBytes = kSub * kUBoxBytes;
+  static constexpr int kVStageBytes = kSub * kVBoxBytes;
   static constexpr int kStageBytes = kUStageBytes + kVStageBytes;
   static constexpr int kRingBytes = STAGES * kStageBytes;
   // Epilogue staging for TMA stores: per epilogue warp two 32-row x 128-byte swizzled images (tiles >= 64 wide only).
@@ -264,9 +269,9 @@ __device__ __forceinline__ float load_in_as_float(const void* ptr, long long i, 
   return __half2float(reinterpret_cast<const __half*>(ptr)[i]);
 }
 
-template <int TILE_Q, int STAGES, int CG>
+template <int TILE_Q, int STAGES, int CG, int TK>
 __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __grid_constant__ GemmParams p) {
-  using L = SmemLayout<TILE_Q, STAGES, CG>;
+  using L = SmemLayout<TILE_Q, STAGES, CG, TK>;
   constexpr int CW = TILE_Q >= 32 ? 32 : 16;  // columns per tcgen05.ld
   constexpr int NCHUNK = TILE_Q / CW;
   constexpr uint32_t kTmemCols = (2 * TILE_Q) < 32 ? 32 : 2 * TILE_Q;  // power of two for every TILE_Q in the menu
@@ -373,8 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
           uint32_t fb = full_bar(stage);
           if constexpr (CG == 2) fb = mapa_cluster(fb, 0);
           const uint32_t su = base + stage * L::kStageBytes;
-          const uint32_t sv = su + kUStageBytes;
-          const int k0 = kb * kTileK;
+          const uint32_t sv = su + L::kUStageBytes;
           if (elect_one()) {
             if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), kTxBytes);
             auto load = [&](uint32_t dst, const void* map, int x, int y) {
@@ -383,17 +387,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
               else
                 tma_load_2d(dst, map, x, y, fb);
             };
-            if (!p.u_mn_major) {
-              load(su, &p.tmap_u, k0, p0);
-            } else {
-              load(su, &p.tmap_u, p0, k0);
-              load(su + 8192u, &p.tmap_u, p0 + 64, k0);
-            }
-            if (!p.v_mn_major) {
-              load(sv, &p.tmap_v, k0, q0);
-            } else {
 #pragma unroll
-              for (int j = 0; j < (kVRows >= 64 ? kVRows / 64 : 1); ++j) load(sv + 8192u * j, &p.tmap_v, q0 + 64 * j, k0);
+            for (int sub = 0; sub < L::kSub; ++sub) {
+              const int k0 = kb * TK + sub * kBoxK;
+              const uint32_t bu = su + sub * kUBoxBytes, bv = sv + sub * L::kVBoxBytes;
+              if (!p.u_mn_major) {
+                load(bu, &p.tmap_u, k0, p0);
+              } else {
+                load(bu, &p.tmap_u, p0, k0);
+                load(bu + 8192u, &p.tmap_u, p0 + 64, k0);
+              }
+              if (!p.v_mn_major) {
+                load(bv, &p.tmap_v, k0, q0);
+              } else {
+#pragma unroll
+                for (int j = 0; j < (kVRows >= 64 ? kVRows / 64 : 1); ++j) load(bv + 8192u * j, &p.tmap_v, q0 + 64 * j, k0);
+              }
             }
           }
           __syncwarp();
@@ -479,9 +488,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
           if (tracing) c1 = clock64();
           if (kb == 0 && lane == 0) trace_stamp(p, 1, it, 1);
           const uint32_t su = base + stage * L::kStageBytes;
-          const uint32_t sv = su + kUStageBytes;
-          const uint64_t du = (uint64_t(p.u_desc_hi) << 32) | uint64_t(p.u_desc_lo | ((su >> 4) & 0x3fffu));
-          const uint64_t dv = (uint64_t(p.v_desc_hi) << 32) | uint64_t(p.v_desc_lo | ((sv >> 4) & 0x3fffu));
+          const uint32_t sv = su + L::kUStageBytes;
           // Probe the next stage now; the answer is collected after the MMAs below have been issued.
           const int nstage = stage + 1 == STAGES ? 0 : stage + 1;
           const uint32_t nphase = stage + 1 == STAGES ? phase ^ 1u : phase;
@@ -489,9 +496,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
           if (lane == 0) next_ready = mbar_try_wait(full_bar(nstage), nphase) ? 1 : 0;
           if (elect_one()) {
 #pragma unroll
-            for (int j = 0; j < kTileK / kUmmaK; ++j) {
-              umma_f16<CG>(d_tmem, du + uint64_t(j * p.u_kstep), dv + uint64_t(j * p.v_kstep), p.idesc,
-                           (kb | j) != 0 ? 1u : 0u);
+            for (int sub = 0; sub < L::kSub; ++sub) {
+              const uint32_t bu = su + sub * kUBoxBytes, bv = sv + sub * L::kVBoxBytes;
+              const uint64_t du = (uint64_t(p.u_desc_hi) << 32) | uint64_t(p.u_desc_lo | ((bu >> 4) & 0x3fffu));
+              const uint64_t dv = (uint64_t(p.v_desc_hi) << 32) | uint64_t(p.v_desc_lo | ((bv >> 4) & 0x3fffu));
+#pragma unroll
+              for (int j = 0; j < kBoxK / kUmmaK; ++j) {
+                umma_f16<CG>(d_tmem, du + uint64_t(j * p.u_kstep), dv + uint64_t(j * p.v_kstep), p.idesc,
+                             (kb | sub | j) != 0 ? 1u : 0u);
+              }
             }
             if (tracing) c3 = clock64();
             // Frees the stage, in every CTA of the pair, once these MMAs have read it.
@@ -921,6 +934,49 @@ __global__ void cast_bias_rows_kernel(const float* __restrict__ in, void* __rest
   const long long total4 = rows * (long long)cols / 4;  // cols % 4 == 0 is checked by the host
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
     float4 x = __ldcs(reinterpret_cast<const float4*>(in) + i);
+    if (bias != nullptr) {
+      const int c = (int)((i * 4) % cols);
+      x.x += load_in_as_float(bias, c, bias_dtype);
+      x.y += load_in_as_float(bias, c + 1, bias_dtype);
+      x.z += load_in_as_float(bias, c + 2, bias_dtype);
+      x.w += load_in_as_float(bias, c + 3, bias_dtype);
+    }
+    if (out_dtype == 1) {
+      reinterpret_cast<float4*>(out)[i] = x;
+    } else if (out_dtype == 2) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+      reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    } else {
+      __half2 lo = __floats2half2_rn(x.x, x.y), hi = __floats2half2_rn(x.z, x.w);
+      reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// out[rows, cols] = cast(sum over s < n_slots of slots[s * slot_stride + ...] + bias[cols]); every slot is a
+// row-major contiguous fp32 [rows, cols] image. Owner-side reduction of the fused K-sharded multi-GPU mode: slot s
+// was filled over NVLink by rank s's GEMM epilogue (peer stores), slot `own` by this GPU's GEMM. The slots are
+// summed in index order, so every rank's result is bitwise independent of arrival order.
+__global__ void reduce_slots_kernel(const float* __restrict__ slots, long long slot_stride, int n_slots,
+                                    void* __restrict__ out, const void* __restrict__ bias, long long rows, int cols,
+                                    int out_dtype, int bias_dtype) {
+  const long long total4 = rows * (long long)cols / 4;  // cols % 4 == 0 is checked by the host
+  const long long stride4 = slot_stride / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+    const float4* src = reinterpret_cast<const float4*>(slots) + i;
+    float4 x = __ldcs(src);
+    int s = 1;
+    for (; s + 4 <= n_slots; s += 4) {  // four independent loads in flight per thread
+      const float4 a = __ldcs(src + s * stride4), b = __ldcs(src + (s + 1) * stride4);
+      const float4 c = __ldcs(src + (s + 2) * stride4), d = __ldcs(src + (s + 3) * stride4);
+      x.x = (((x.x + a.x) + b.x) + c.x) + d.x, x.y = (((x.y + a.y) + b.y) + c.y) + d.y;
+      x.z = (((x.z + a.z) + b.z) + c.z) + d.z, x.w = (((x.w + a.w) + b.w) + c.w) + d.w;
+    }
+    for (; s < n_slots; ++s) {
+      const float4 a = __ldcs(src + s * stride4);
+      x.x += a.x, x.y += a.y, x.z += a.z, x.w += a.w;
+    }
     if (bias != nullptr) {
       const int c = (int)((i * 4) % cols);
       x.x += load_in_as_float(bias, c, bias_dtype);

@@ -216,6 +216,7 @@ def _fill_args(a, b, out, bias, pol: _policy.Policy, a_t: bool, b_t: bool) -> _l
     p.max_ctas = pol.max_ctas
     p.stream_k = 1 if pol.stream_k else 0
     p.no_pdl = 0 if pol.pdl else 1
+    p.tile_k = pol.tile_k
     return args
 
 
@@ -392,6 +393,56 @@ def gemm_a16w16(
     else:
         lib.b200_gemm_release(handle)
     return out
+
+
+def gemm_a16w16_to_pointer(a: torch.Tensor, b: torch.Tensor, out_ptr: int, out_dtype: torch.dtype, user_kwargs: dict = {},
+                           stream: Optional[torch.cuda.Stream] = None, layout: str = "nt") -> None:
+    """The same product as `gemm_a16w16` (no bias), written to the raw device address `out_ptr`: an M x N
+    row-major contiguous image of `out_dtype` that kernels on a's device can store to. This is how the fused
+    K-sharded mode lets the epilogue write its tiles straight into another GPU's receive buffer over NVLink
+    (`out_ptr` then comes from b200_peer_open). The caller owns the memory behind `out_ptr` and its lifetime."""
+    layout = layout.lower()
+    assert layout in ("nn", "nt", "tn", "tt") and a.is_cuda and a.device == b.device and a.dtype == b.dtype
+    assert out_dtype in (a.dtype, torch.float32) and out_ptr % 16 == 0
+    device = a.device
+    if stream is None:
+        stream = torch.cuda.current_stream(device)
+    kw_key = tuple(sorted(user_kwargs.items())) if user_kwargs else ()
+    key = ("ptr", a.data_ptr(), a.shape, a.stride(), a.dtype, b.data_ptr(), b.shape, b.stride(), out_ptr, out_dtype,
+           kw_key, stream.cuda_stream, layout, device.index)
+    lib = _lib.load()
+    ent = _prepared.get(key)
+    dev_index = device.index if device.index is not None else torch.cuda.current_device()
+    if ent is None or ent.ws_gen != ent.ws.generation:
+        a_t, b_t = layout[0] == "t", layout[1] == "t"
+        m, k = a.shape
+        n = b.shape[1]
+        assert b.shape[0] == k and m > 0 and n > 0 and k > 0
+        _check_operand("A", a, a_t, False, m)
+        _check_operand("B", b, b_t, False, None)
+        pol = resolve_policy(m, n, k, a.dtype, layout, user_kwargs, _num_sms(device))
+        why = _policy.validate(pol, m, n, k, layout)
+        assert why is None, f"unsupported gemm_a16w16 shape/config: {why}"
+        args = _fill_args(a, b, torch.empty(0, dtype=out_dtype), None, pol, a_t, b_t)
+        args.out = out_ptr
+        ws = _workspace_for(device, stream)
+        with torch.cuda.device(dev_index):
+            need = lib.b200_gemm_workspace_bytes(C.byref(args))
+            if need:
+                ws.ensure(need, device, stream)
+                args.workspace = ws.buf.data_ptr()
+                args.workspace_bytes = ws.buf.numel()
+            args.status = ws.status.data_ptr()
+            handle = C.c_void_p()
+            rc = lib.b200_gemm_prepare(C.byref(args), C.byref(handle))
+        if rc != 0:
+            raise RuntimeError(f"b200_gemm_prepare failed ({rc}): {_lib.strerror(rc)}")
+        ent = _Prepared(handle, ws, dev_index, n)
+        _remember(key, ent)
+    with torch.cuda.device(ent.dev):
+        rc = lib.b200_gemm_launch(ent.handle, C.c_void_p(stream.cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"b200_gemm_launch failed ({rc}): {_lib.strerror(rc)}")
 
 
 def plan(a: torch.Tensor, b: torch.Tensor, layout: str = "nt", user_kwargs: dict = {},

@@ -1,6 +1,6 @@
 """Single-box multi-GPU partitioning of one large GEMM (one process per GPU, torch.distributed for plumbing).
 
-Two modes, neither present in the reference (xytpai/flydsl-examples is single-GPU; its op is
+Three modes, none present in the reference (xytpai/flydsl-examples is single-GPU; its op is
 kernels/gemm_a16w16_gfx950.py:1288):
 
   N-shard  rank r owns B[:, n0:n1] and computes C[:, n0:n1]. A is replicated. No communication at all.
@@ -8,6 +8,9 @@ kernels/gemm_a16w16_gfx950.py:1288):
            kernel (fp32-output path), and the partials are summed across GPUs with an NCCL reduce-scatter over
            NVLink, chunk by chunk along M so the reduce of chunk i overlaps the GEMM of chunk i+1. Each rank ends up
            with 1/world of the rows of every chunk, rounded once (bias added) by a small cast kernel.
+
+  fused K-shard  the same partition, but every rank's GEMM epilogue stores its fp32 tiles straight into the owning
+           rank's receive slots over NVLink (peer memory) and the owner sums its slots; no collective moves data.
 
 `gemm_fn` is the product call everywhere; the CPU tests inject their own function to exercise the partition and
 exchange logic with gloo ranks.
@@ -148,3 +151,130 @@ def gemm_k_sharded(a_local, b_local, out_dtype, bias=None, layout="nt", user_kwa
         exchange.reduce(buf, partial[buf], reduced[buf], out[c * per:(c + 1) * per])
     exchange.finish()
     return KShardResult(out=out, row_ranges=ranges, reduce_bytes=4 * m * n * (world - 1) // world)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Fused K-shard: the GEMM epilogue itself moves the partial sums over NVLink.
+#
+# Rows of C are owned in contiguous blocks (rank d owns rows [d*per, (d+1)*per)). Every rank keeps `sets` x world
+# fp32 receive slots of [per, N]; slot s of rank d is written only by rank s. Rank r runs one GEMM per destination d
+# — A_r[rows of d] @ B_r with fp32 output — whose `out` is slot r of rank d mapped into r's address space, so the
+# epilogue's stores cross NVLink tile by tile while the tensor cores work on the next tile; destinations are visited
+# in the order r+1, r+2, ..., r, so that at any moment the ranks send to different peers. One stream-ordered barrier
+# later the owner sums its slots in index order (+ bias) and rounds once. With two slot sets alternating between
+# calls, the barrier of call c+1 also proves that every rank has finished reading the set of call c, so one barrier
+# per call is enough. No kernel ever waits on another GPU.
+class PeerSlots:
+    """Receive slots of the fused K-shard mode on CUDA devices: local memory exported with CUDA IPC and every peer's
+    slots mapped into this process (b200_peer_export / b200_peer_open). Collective over `group`: every rank must
+    construct it with the same sizes. Keep it for the life of the weights; `close()` unmaps."""
+
+    def __init__(self, rows: int, cols: int, device: torch.device, group=None, sets: int = 2):
+        import torch.distributed as dist
+
+        assert device.type == "cuda", "peer slots live in CUDA device memory"
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.rows, self.cols, self.sets, self.calls = rows, cols, sets, 0
+        self.device = device
+        self.local = torch.empty((sets, self.world, rows, cols), dtype=torch.float32, device=device)
+        lib = _lib.load()
+        mine = _lib.PeerHandle()
+        with torch.cuda.device(device):
+            rc = lib.b200_peer_export(self.local.data_ptr(), C.byref(mine))
+        if rc != 0:
+            raise RuntimeError(f"b200_peer_export failed ({rc}): {_lib.strerror(rc)}")
+        blobs = [None] * self.world
+        dist.all_gather_object(blobs, bytes(mine), group=group)
+        self._handles, self._base = [], []
+        for r, blob in enumerate(blobs):
+            h = _lib.PeerHandle.from_buffer_copy(blob)
+            self._handles.append(h)
+            if r == self.rank:
+                self._base.append(self.local.data_ptr())
+                continue
+            ptr = C.c_void_p()
+            with torch.cuda.device(device):
+                rc = lib.b200_peer_open(C.byref(h), C.byref(ptr))
+            if rc != 0:
+                raise RuntimeError(f"b200_peer_open of rank {r}'s slots failed ({rc}): {_lib.strerror(rc)}")
+            self._base.append(ptr.value)
+        dist.barrier(group=group)  # nobody stores into a peer before every mapping exists
+
+    def next_set(self) -> int:
+        s = self.calls % self.sets
+        self.calls += 1
+        return s
+
+    def target(self, dest: int, set_idx: int, src: int) -> int:
+        """Address, in this process, of slot `src` of set `set_idx` on rank `dest`."""
+        return self._base[dest] + 4 * self.rows * self.cols * (set_idx * self.world + src)
+
+    def local_set(self, set_idx: int) -> torch.Tensor:
+        return self.local[set_idx]
+
+    def close(self) -> None:
+        lib = _lib.load()
+        for r, (h, base) in enumerate(zip(self._handles, self._base)):
+            if r != self.rank and base:
+                with torch.cuda.device(self.device):
+                    lib.b200_peer_close(C.c_void_p(base), C.byref(h))
+        self._base = [0] * self.world
+
+
+def reduce_slots(local_set: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor], stream: torch.cuda.Stream) -> None:
+    """out = cast(sum over slots (index order) + bias) with the library's kernel."""
+    ids = {torch.float32: 1, torch.bfloat16: 2, torch.float16: 3}
+    n_slots, rows, cols = local_set.shape
+    rc = _lib.load().b200_gemm_reduce_slots(
+        local_set.data_ptr(), rows * cols, n_slots, out.data_ptr(), None if bias is None else bias.data_ptr(), rows, cols,
+        ids[out.dtype], 0 if bias is None else ids[bias.dtype], C.c_void_p(stream.cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"b200_gemm_reduce_slots failed ({rc}): {_lib.strerror(rc)}")
+
+
+def fused_send_order(world: int, rank: int) -> list[int]:
+    """Destinations in the order rank `rank` serves them: its right-hand neighbours first, itself last."""
+    return [(rank + j) % world for j in range(1, world + 1)]
+
+
+def gemm_k_sharded_fused(a_local, b_local, out_dtype, slots, bias=None, layout="nt", user_kwargs={}, group=None, out=None,
+                         gemm_into: Optional[Callable] = None, barrier: Optional[Callable] = None,
+                         reduce_fn: Optional[Callable] = None) -> KShardResult:
+    """Row-sharded C = sum over ranks of A[:, k_r] @ B[k_r, :] (+ bias) where the partial sums travel inside the GEMM
+    epilogue (peer stores into `slots`), not in a separate collective. Rank r returns rows [r*M/world, (r+1)*M/world).
+
+    `gemm_into(a_rows, b, target)`, `barrier()` and `reduce_fn(local_set, out, bias)` default to the CUDA path; the
+    CPU tests inject their own to run the schedule with gloo ranks."""
+    import torch.distributed as dist
+
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    m, n = a_local.shape[0], b_local.shape[1]
+    assert m % world == 0, "M must divide by the number of ranks"
+    per = m // world
+    assert (slots.rows, slots.cols, slots.world) == (per, n, world), "slots were built for another problem"
+    dev = a_local.device
+    if gemm_into is None:
+        from .gemm_a16w16 import gemm_a16w16_to_pointer
+
+        def gemm_into(a_rows, b, target):
+            gemm_a16w16_to_pointer(a_rows, b, target, torch.float32, user_kwargs=user_kwargs, layout=layout)
+    if barrier is None:
+        flag = getattr(slots, "_flag", None)
+        if flag is None:
+            flag = slots._flag = torch.zeros(1, dtype=torch.float32, device=dev)
+
+        def barrier():
+            # Stream-ordered on every rank: it cannot complete here before each peer has reached it, i.e. before
+            # the peer's GEMMs (and their stores into this rank's slots) have finished.
+            dist.all_reduce(flag, group=group)
+    if reduce_fn is None:
+        def reduce_fn(local_set, dst, bias_):
+            reduce_slots(local_set, dst, bias_, torch.cuda.current_stream(dev))
+    if out is None:
+        out = torch.empty((per, n), dtype=out_dtype, device=dev)
+    set_idx = slots.next_set()
+    for dest in fused_send_order(world, rank):
+        gemm_into(a_local[dest * per:(dest + 1) * per], b_local, slots.target(dest, set_idx, rank))
+    barrier()
+    reduce_fn(slots.local_set(set_idx), out, bias)
+    return KShardResult(out=out, row_ranges=[(rank * per, (rank + 1) * per)], reduce_bytes=4 * per * n * (world - 1))

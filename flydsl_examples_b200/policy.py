@@ -15,10 +15,26 @@ from pathlib import Path
 from typing import Optional
 
 TILE_M = 128  # rows per CTA on the MMA M axis (TMEM lanes)
-TILE_K = 64   # one 128-byte swizzle span of 16-bit data
+TILE_K = 64   # one TMA box: a 128-byte swizzle span of 16-bit data
 TILE_N_MENU = (16, 32, 64, 128, 256)
-MAX_STAGES = {16: 10, 32: 10, 64: 8, 128: 6, 256: 4}          # one CTA per tile
+MAX_STAGES = {16: 5, 32: 5, 64: 4, 128: 3, 256: 4}            # one CTA per tile, default stage depth
+MAX_STAGES_K64 = {16: 8, 32: 8, 64: 8, 128: 6, 256: 4}        # one CTA per tile, 64-deep stages
 MAX_STAGES_PAIR = {128: 8, 256: 6}                            # a CTA pair per 256-row tile (cta_group 2)
+
+
+def tile_k(tile_n: int, cta_group: int = 1, requested: int = 0) -> int:
+    """K elements per pipeline stage of a variant. Single-CTA tiles up to 128 wide exist with 64- and 128-deep
+    stages (two 64-deep boxes per operand and stage, so that the fixed per-stage cost — barrier poll, election,
+    commit — is paid once per 128); 128 is their default. 256-wide tiles and CTA pairs are 64-deep only."""
+    if cta_group == 1 and tile_n <= 128:
+        return requested if requested in (64, 128) else 128
+    return 64
+
+
+def max_stages(tile_n: int, cta_group: int = 1, requested_tile_k: int = 0) -> int:
+    if cta_group == 2:
+        return MAX_STAGES_PAIR[tile_n]
+    return (MAX_STAGES_K64 if tile_k(tile_n, 1, requested_tile_k) == 64 else MAX_STAGES)[tile_n]
 SMEM_LIMIT = 232448
 TMEM_COLUMNS = 512
 NUM_SMS_DEFAULT = 148
@@ -29,7 +45,7 @@ REFERENCE_KEYS = (
     "use_half_tile_interleaved",
 )
 # Keys that only exist here.
-BLACKWELL_KEYS = ("tile_n", "swap_ab", "cta_group", "split_mode", "max_ctas", "stream_k")
+BLACKWELL_KEYS = ("tile_n", "swap_ab", "cta_group", "split_mode", "max_ctas", "stream_k", "tile_k")
 # Keys that switch behaviour without describing a tiling (they do not make a dict a "Blackwell policy").
 CONTROL_KEYS = ("strict_reference_envelope", "pdl")
 SPLIT_MODES = {"ticket": 0, "cluster": 2}
@@ -47,22 +63,25 @@ class Policy:
     max_ctas: int = 0
     stream_k: bool = False
     pdl: bool = True         # programmatic dependent launch: set-up overlaps the previous kernel in the stream
+    tile_k: int = 0          # K elements per pipeline stage; 0 = the tile's default (see tile_k())
 
     def as_dict(self) -> dict:
         return asdict(self)
 
 
-def smem_bytes(tile_n: int, stages: int, cta_group: int = 1) -> int:
+def smem_bytes(tile_n: int, stages: int, cta_group: int = 1, requested_tile_k: int = 0) -> int:
     """Dynamic shared memory of one CTA: the ring, the bias slice, the barriers and alignment slack. In a pair
     each CTA holds 128 of the tile's 256 rows and half of its tile_n columns."""
     staging = 4 * 2 * 32 * 128 if tile_n >= 64 else 0  # epilogue images for TMA stores
     staging = max(staging, TILE_M * tile_n * 4 if tile_n <= 64 else 0)  # rows received in cluster split-K mode
-    return stages * (TILE_M * TILE_K * 2 + (tile_n // cta_group) * TILE_K * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024
+    tk = tile_k(tile_n, cta_group, requested_tile_k)
+    return stages * (TILE_M * tk * 2 + (tile_n // cta_group) * tk * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024
 
 
-def split_k_slices(k: int, split_k: int) -> list[tuple[int, int]]:
-    """K-block ranges [(first_block, n_blocks)] of each slice: uneven slices allowed, none empty."""
-    kb = (k + TILE_K - 1) // TILE_K
+def split_k_slices(k: int, split_k: int, tk: int = TILE_K) -> list[tuple[int, int]]:
+    """K-block ranges [(first_block, n_blocks)] of each slice, in blocks of `tk` elements (the variant's stage
+    depth): uneven slices allowed, none empty."""
+    kb = (k + tk - 1) // tk
     split_k = max(1, min(split_k, kb))
     base, rem = divmod(kb, split_k)
     out = []
@@ -138,10 +157,10 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
     stage_menu = MAX_STAGES if pol.cta_group == 1 else MAX_STAGES_PAIR
     if pol.tile_n not in stage_menu:
         return f"cta_group 2 needs tile_n in {tuple(MAX_STAGES_PAIR)}, got {pol.tile_n}"
-    if pol.stages < 0 or pol.stages == 1 or pol.stages > stage_menu[pol.tile_n]:
-        return f"stages must be 0 (auto) or 2..{stage_menu[pol.tile_n]} for tile_n={pol.tile_n}, got {pol.stages}"
-    if pol.stages and smem_bytes(pol.tile_n, pol.stages, pol.cta_group) > SMEM_LIMIT:
-        return "shared memory ring exceeds 227 KB"
+    if pol.stages < 0 or pol.stages == 1:
+        return f"stages must be 0 (auto) or >= 2, got {pol.stages} (more than fit are clamped)"
+    if pol.tile_k not in (0, tile_k(pol.tile_n, pol.cta_group, pol.tile_k)):
+        return f"tile_k {pol.tile_k} is not built for tile_n {pol.tile_n}, cta_group {pol.cta_group}"
     if pol.split_k < 1:
         return f"split_k must be >= 1, got {pol.split_k}"
     if pol.split_mode not in SPLIT_MODES:

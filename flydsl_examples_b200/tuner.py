@@ -39,16 +39,17 @@ def tile_fit(m: int, n: int, k: int, cfg: dict) -> float:
     tm = P.TILE_M * cfg.get("cta_group", 1)
     pad_p = -(-p_ext // tm) * tm
     pad_q = -(-q // cfg["tile_n"]) * cfg["tile_n"]
-    pad_k = sum(nb for _, nb in P.split_k_slices(k, cfg.get("split_k", 1))) * P.TILE_K
+    tk = P.tile_k(cfg["tile_n"], cfg.get("cta_group", 1), cfg.get("tile_k", 0))
+    pad_k = sum(nb for _, nb in P.split_k_slices(k, cfg.get("split_k", 1), tk)) * tk
     return (m * n * k) / (pad_p * pad_q * pad_k)
 
 
 def candidate_configs(args: TuneArgs, num_sms: int = P.NUM_SMS_DEFAULT) -> list[dict]:
     """Every runnable policy worth timing for this problem."""
-    kb = -(-args.k // P.TILE_K)
-    variants = [(1, t) for t in P.TILE_N_MENU] + [(2, t) for t in P.MAX_STAGES_PAIR]
+    variants = [(1, t, tk) for t in P.TILE_N_MENU for tk in ((64, 128) if t <= 128 else (64,))]
+    variants += [(2, t, 64) for t in P.MAX_STAGES_PAIR]
     out = []
-    for (cg, tile_n), swap in itertools.product(variants, (False, True)):
+    for (cg, tile_n, tk), swap in itertools.product(variants, (False, True)):
         if swap and (cg == 2 or args.m > 256):
             continue
         p_ext, q = (args.n, args.m) if swap else (args.m, args.n)
@@ -56,7 +57,8 @@ def candidate_configs(args: TuneArgs, num_sms: int = P.NUM_SMS_DEFAULT) -> list[
             continue  # tile far wider than the problem
         tiles = -(-p_ext // (P.TILE_M * cg)) * -(-q // tile_n)
         walkers = num_sms // cg
-        max_stages = (P.MAX_STAGES if cg == 1 else P.MAX_STAGES_PAIR)[tile_n]
+        kb = -(-args.k // tk)  # K blocks of this variant's stage depth
+        max_stages = P.max_stages(tile_n, cg, tk)
         stage_opts = sorted({max_stages, max(2, max_stages - 2)})
         splits = [(1, False, "ticket")]
         if tiles % walkers != 0:
@@ -72,9 +74,9 @@ def candidate_configs(args: TuneArgs, num_sms: int = P.NUM_SMS_DEFAULT) -> list[
         groups = (0, 4, 8) if tiles >= 2 * walkers else (0,)
         for stages, (split_k, stream_k, mode), group_m in itertools.product(stage_opts, splits, groups):
             cfg = {"tile_n": tile_n, "cta_group": cg, "stages": stages, "split_k": split_k, "stream_k": stream_k,
-                   "group_m": group_m, "swap_ab": swap, "split_mode": mode}
+                   "group_m": group_m, "swap_ab": swap, "split_mode": mode, "tile_k": tk}
             pol = P.Policy(tile_n=tile_n, stages=stages, split_k=split_k, group_m=group_m, swap_ab=swap, cta_group=cg,
-                           stream_k=stream_k, split_mode=mode)
+                           stream_k=stream_k, split_mode=mode, tile_k=tk)
             if P.validate(pol, args.m, args.n, args.k, args.layout) is None:
                 out.append(cfg)
     if not out:

@@ -47,8 +47,9 @@ extern "C" {
 /* Blackwell policy. Replaces the reference's compile-time GemmA16W16Gfx950Param
  * (kernels/gemm_a16w16_gfx950.py:33-61): block_m/n/k, stages, split_k, *_waves, group_m, HTI flag. */
 typedef struct b200_gemm_policy {
-  int32_t tile_n;     /* MMA N extent of one CTA tile: 16, 32, 64, 128 or 256 (tile M is 128 per CTA; K step 64) */
-  int32_t stages;     /* depth of the TMA->smem ring; 0 = as many as fit in 227 KB                                */
+  int32_t tile_n;     /* MMA N extent of one CTA tile: 16, 32, 64, 128 or 256 (tile M is 128 per CTA; the K extent of
+                         a pipeline stage follows from the variant, see b200_gemm_describe_variant)                */
+  int32_t stages;     /* depth of the TMA->smem ring; 0, or more than fit in 227 KB, = as many as fit              */
   int32_t split_k;    /* >= 1 K-slices per output tile (uneven slices allowed, K tail is zero-filled by TMA)      */
   int32_t group_m;    /* grouped rasterisation: tiles are walked in groups of group_m tile rows; 0 = row-major     */
   int32_t swap_ab;    /* 1: compute C^T = B^T A^T so N sits on the 128-row MMA axis (small-M shapes)               */
@@ -59,7 +60,9 @@ typedef struct b200_gemm_policy {
   int32_t no_pdl;     /* 1: launch without programmatic dependent launch. By default the kernel's set-up (barriers,
                          TMEM, descriptor prefetch) may overlap the end of the previous kernel in the stream; it
                          waits for that kernel to complete before it reads or writes global memory               */
-  int32_t reserved[6];
+  int32_t tile_k;     /* K elements per pipeline stage: 64 or 128 where the variant table has both (single-CTA tiles up
+                         to 128 wide); 0 = the tile's default (128 there, 64 for 256-wide tiles and CTA pairs)      */
+  int32_t reserved[5];
 } b200_gemm_policy;
 
 /* One GEMM call. Replaces the argument list of the reference's jit host stub gemm_a16w16_gfx950
@@ -149,10 +152,11 @@ int b200_gemm_plan_query(const b200_gemm_args* args, b200_gemm_plan* plan);
  * (kernels/gemm_a16w16_gfx950.py:1277-1281), whose fixed 2 x int32[256] limited split-K to 256 tiles. */
 uint64_t b200_gemm_workspace_bytes(const b200_gemm_args* args);
 
-/* Kernel variant table (for the tuner): number of compiled (tile_n, cta_group) variants and their description.
+/* Kernel variant table (for the tuner): number of compiled (tile_n, cta_group, tile_k) variants and their
+ * description (tile_k = K elements per pipeline stage; the first entry of a (tile_n, cta_group) is its default).
  * Replaces the JIT cache of kernels/common.py:7-39 with an ahead-of-time table. */
 int b200_gemm_num_variants(void);
-int b200_gemm_describe_variant(int index, int32_t* tile_n, int32_t* cta_group, int32_t* max_stages);
+int b200_gemm_describe_variant(int index, int32_t* tile_n, int32_t* cta_group, int32_t* max_stages, int32_t* tile_k);
 
 /* out[rows, cols] = cast(in[rows, cols] (fp32) + bias[cols]); row-major contiguous, cols % 4 == 0, 16-byte aligned
  * pointers. Last step of the K-sharded multi-GPU mode (fp32 partial sums reduced over NVLink, then rounded once).
@@ -160,6 +164,35 @@ int b200_gemm_describe_variant(int index, int32_t* tile_n, int32_t* cta_group, i
  * :660-661); the reference itself has no multi-GPU path. */
 int b200_gemm_cast_bias(const float* in, void* out, const void* bias, int64_t rows, int64_t cols, int32_t out_dtype,
                         int32_t bias_dtype, void* cuda_stream);
+
+/* Fused K-sharded mode (several GPUs of one box, one process per GPU; not in the reference, which is single-GPU).
+ * Rank r computes the fp32 partial product of its K slab for the rows that rank d owns and its GEMM epilogue stores
+ * the tiles straight into slot r of rank d's receive buffer over NVLink: `out` of b200_gemm_a16w16 is then a pointer
+ * returned by b200_peer_open. After all ranks have finished (a stream-ordered barrier of the host's choosing), the
+ * owner sums its slots in index order, adds the bias and rounds once:
+ * out[rows, cols] = cast(sum_s slots[s * slot_stride ...][rows, cols] + bias[cols]); slots are fp32 row-major
+ * contiguous images slot_stride elements apart (slot_stride % 4 == 0), cols % 4 == 0, 16-byte aligned pointers.
+ * Same rounding as the reference epilogue (kernels/gemm_a16w16_gfx950.py:541-550, :660-661). */
+int b200_gemm_reduce_slots(const float* slots, int64_t slot_stride, int32_t n_slots, void* out, const void* bias,
+                           int64_t rows, int64_t cols, int32_t out_dtype, int32_t bias_dtype, void* cuda_stream);
+
+/* Peer mapping of device memory between the processes of one box (CUDA IPC). The exporting process fills a handle for
+ * any pointer inside a cudaMalloc allocation (it need not be the allocation's base); the handle is plain bytes and may
+ * be sent to the other processes by any host channel. b200_peer_open maps it into the calling process for the current
+ * device (peer access to the exporting GPU is enabled on first use) and returns the pointer that corresponds to the
+ * exported one; a process cannot open its own handle. b200_peer_close unmaps. These calls allocate no device memory and
+ * launch nothing; the exporter must keep the allocation alive while any peer has it open. Kernels may store to such a pointer
+ * and load from it one CTA at a time; a load that fans one fetch out to several CTAs of a cluster must never target it. */
+typedef struct b200_peer_handle {
+  uint8_t ipc[64];  /* cudaIpcMemHandle_t of the containing allocation */
+  uint64_t offset;  /* byte offset of the exported pointer inside it   */
+  uint64_t bytes;   /* bytes from the exported pointer to the end of the allocation */
+  int32_t device;   /* CUDA device ordinal in the exporting process    */
+  int32_t reserved;
+} b200_peer_handle;
+int b200_peer_export(const void* ptr, b200_peer_handle* handle);
+int b200_peer_open(const b200_peer_handle* handle, void** ptr);
+int b200_peer_close(void* ptr, const b200_peer_handle* handle);
 
 /* Text for an error code; for B200_GEMM_ERR_LAUNCH the last CUDA error string seen by this thread. */
 const char* b200_gemm_strerror(int code);

@@ -12,7 +12,7 @@ def _declared():
     names = set()
     for h in sorted((ROOT / "include").glob("*.h")):
         text = re.sub(r"/\*.*?\*/", "", h.read_text(), flags=re.S)
-        names |= set(re.findall(r"\b(b200_gemm_[a-z0-9_]+)\s*\(", text))
+        names |= set(re.findall(r"\b(b200_(?:gemm|peer)_[a-z0-9_]+)\s*\(", text))
     return names
 
 
@@ -32,6 +32,7 @@ def test_version_variants_and_strerror():
     assert b"sm_100a" in lib.b200_gemm_version()
     v = _lib.variants()
     assert {x["tile_n"] for x in v} == {16, 32, 64, 128, 256}
+    assert {(x["tile_n"], x["cta_group"], x["tile_k"]) for x in v} >= {(128, 1, 128), (128, 1, 64), (16, 1, 64), (256, 1, 64), (256, 2, 64)}
     assert _lib.strerror(0) == "ok"
     assert "policy" in _lib.strerror(-2)
     assert "unknown" in _lib.strerror(-99)

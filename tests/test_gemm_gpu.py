@@ -307,6 +307,19 @@ def test_narrow_tiles_k_contiguous(tile_n, swap):
                         user_kwargs={"tile_n": tile_n, "swap_ab": swap, "split_k": 5}))
 
 
+@pytest.mark.parametrize("tile_k", [64, 128])
+@pytest.mark.parametrize("tile_n", [16, 32, 64, 128])
+def test_both_stage_depths(tile_n, tile_k):
+    # Single-CTA tiles up to 128 wide are built with 64- and 128-deep pipeline stages; K = 1000 leaves a ragged
+    # last stage in both, and the split and cluster modes see uneven slices.
+    for layout in (LAYOUTS if tile_n >= 64 else ("nt",)):
+        for extra in ({}, {"split_k": 3}, {"split_k": 4, "split_mode": "cluster"}):
+            kw = {"tile_n": tile_n, "tile_k": tile_k, **extra}
+            case = O.Case("depth", "bf16", layout, 200, 264, 1000, seed=tile_n + tile_k, bias_std=0.2,
+                          out_dtype="fp32" if extra else None, user_kwargs=kw)
+            run_case(case)
+
+
 @pytest.mark.parametrize("layout", LAYOUTS)
 def test_exhaustive_edge_residues(layout):
     # every residue class of M mod 8 and N mod 8 around one tile, K around one K block

@@ -92,7 +92,7 @@ def test_reference_policy_keys_are_accepted():
     assert P.validate(pol, 64, 64, 512, "nt") is None
     assert make_gemm_a16w16_param_and_validate(64, 64, 512, dict(kw, a_is_transposed=False, b_is_transposed=True)) is not None
     assert make_gemm_a16w16_param_and_validate(64, 64, 512, {"tile_n": 48}) is None
-    assert make_gemm_a16w16_param_and_validate(64, 64, 512, {"tile_n": 256, "stages": 9}) is None
+    assert make_gemm_a16w16_param_and_validate(64, 64, 512, {"tile_n": 256, "stages": 1}) is None
 
 
 def test_blackwell_policy_is_taken_literally():
@@ -106,11 +106,19 @@ def test_validate_rules():
     assert P.validate(P.Policy(tile_n=32), 32, 384, 512, "nn") is not None  # N-contiguous B on a 32-wide tile
     assert P.validate(P.Policy(tile_n=64), 32, 384, 512, "nn") is None
     assert P.validate(P.Policy(tile_n=32, swap_ab=True), 32, 384, 512, "tn") is not None  # M-contiguous A after swap
-    assert P.validate(P.Policy(tile_n=256, stages=5), 512, 512, 512, "nt") is not None
+    assert P.validate(P.Policy(tile_n=256, stages=1), 512, 512, 512, "nt") is not None
     assert P.validate(P.Policy(tile_n=256, stages=4), 512, 512, 512, "nt") is None
+    assert P.validate(P.Policy(tile_n=256, stages=9), 512, 512, 512, "nt") is None  # clamped to what fits
     assert P.validate(P.Policy(tile_n=128, split_k=0), 512, 512, 512, "nt") is not None
     for t in P.TILE_N_MENU:
         assert P.smem_bytes(t, P.MAX_STAGES[t]) <= P.SMEM_LIMIT
+        assert P.smem_bytes(t, P.MAX_STAGES_K64[t], 1, 64) <= P.SMEM_LIMIT
+    for t, st in P.MAX_STAGES_PAIR.items():
+        assert P.smem_bytes(t, st, 2) <= P.SMEM_LIMIT
+    assert (P.tile_k(128), P.tile_k(256), P.tile_k(128, 2), P.tile_k(128, 1, 64)) == (128, 64, 64, 64)
+    assert P.validate(P.Policy(tile_n=256, tile_k=128), 512, 512, 512, "nt") is not None
+    assert P.validate(P.Policy(tile_n=64, tile_k=64), 512, 512, 512, "nt") is None
+    assert (P.max_stages(128), P.max_stages(128, 1, 64), P.max_stages(128, 2)) == (3, 6, 8)
 
 
 def test_heuristic_is_always_valid():
@@ -123,10 +131,10 @@ def test_heuristic_is_always_valid():
 
 
 def test_split_k_slices_cover_k_exactly_once():
-    for k in (1, 63, 64, 65, 1000, 4100, 7168):
+    for k, tk in ((1, 64), (63, 64), (64, 128), (65, 64), (1000, 128), (4100, 64), (4100, 128), (7168, 128)):
         for s in (1, 2, 3, 7, 8, 16, 32, 200):
-            sl = P.split_k_slices(k, s)
-            kb = (k + 63) // 64
+            sl = P.split_k_slices(k, s, tk)
+            kb = (k + tk - 1) // tk
             assert len(sl) == min(s, kb)
             assert all(n >= 1 for _, n in sl)
             assert sl[0][0] == 0 and sum(n for _, n in sl) == kb
@@ -153,6 +161,9 @@ def test_plan_query_on_cpu_tensors():
     b = torch.empty(4096, 4096, dtype=torch.bfloat16).t()
     pl = plan(a, b, "nt", {"tile_n": 256, "group_m": 8})
     assert (pl["tile_m"], pl["tile_n"], pl["tile_k"], pl["stages"]) == (128, 256, 64, 4)
+    assert plan(a, b, "nt", {"tile_n": 128})["tile_k"] == 128 and plan(a, b, "nt", {"tile_n": 128, "cta_group": 2})["tile_k"] == 64
+    pl64 = plan(a, b, "nt", {"tile_n": 128, "tile_k": 64})
+    assert (pl64["tile_k"], pl64["stages"]) == (64, 6)
     assert pl["tiles_p"] * pl["tiles_q"] == 256 and pl["num_units"] == 256
     assert pl["workspace_bytes"] == 0 and pl["tmem_cols"] == 512
     assert pl["smem_bytes"] == P.smem_bytes(256, 4) <= P.SMEM_LIMIT
@@ -160,9 +171,9 @@ def test_plan_query_on_cpu_tensors():
               {"tile_n": 32, "swap_ab": True, "split_k": 16}, out_dtype=torch.float32)
     assert pl["swap_ab"] == 1 and pl["tiles_p"] == 3 and pl["tiles_q"] == 1 and pl["num_units"] == 48
     assert pl["partial_bytes"] == 48 * 128 * 32 * 4 and pl["counter_bytes"] == 1 << 20
-    # split_k larger than the number of K blocks is clamped
-    pl = plan(torch.empty(64, 100, dtype=torch.float16), torch.empty(100, 64, dtype=torch.float16), "nn", {"tile_n": 64, "split_k": 9})
-    assert pl["split_k"] == 2
+    # split_k larger than the number of K blocks (128 deep for this tile) is clamped
+    pl = plan(torch.empty(64, 300, dtype=torch.float16), torch.empty(300, 64, dtype=torch.float16), "nn", {"tile_n": 64, "split_k": 9})
+    assert pl["split_k"] == 3
 
 
 def test_plan_flags_operands_tma_cannot_describe():
@@ -227,7 +238,8 @@ def test_stream_k_plan_matches_the_library():
         b = torch.empty(n, k, dtype=torch.bfloat16).t()
         pl = plan(a, b, "nt", {"tile_n": tile_n, "stream_k": True})
         tiles = pl["tiles_p"] * pl["tiles_q"]
-        grid, sk_tiles, sk_slots = P.stream_k_plan(tiles, (k + 63) // 64, 148)
+        tk = P.tile_k(tile_n)
+        grid, sk_tiles, sk_slots = P.stream_k_plan(tiles, (k + tk - 1) // tk, 148)
         assert (pl["grid"], pl["sk_tiles"], pl["sk_slots"]) == (grid, sk_tiles, sk_slots), (m, n, k)
         assert pl["stream_k"] == (1 if sk_tiles else 0)
         if sk_tiles:

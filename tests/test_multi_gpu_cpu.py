@@ -116,3 +116,89 @@ def test_two_rank_gloo_n_shard_and_k_shard():
         for r0, r1 in ranges:
             rows |= set(range(r0, r1))
     assert rows == set(range(64))  # every row of C is owned by exactly one rank
+
+
+# ------------------------------------------------------------------------------------------- fused K-shard schedule
+class _SharedSlots:
+    """Test double for PeerSlots: every rank's receive slots live in one shared-memory tensor
+    [rank, set, slot, rows, cols], so a 'peer store' is a plain write by another process."""
+
+    def __init__(self, shared, rank):
+        self.shared, self.rank = shared, rank
+        self.world, self.sets, _, self.rows, self.cols = (shared.shape[0], shared.shape[1], shared.shape[2],
+                                                          shared.shape[3], shared.shape[4])
+        self.calls = 0
+
+    def next_set(self):
+        s = self.calls % self.sets
+        self.calls += 1
+        return s
+
+    def target(self, dest, set_idx, src):
+        return self.shared[dest, set_idx, src]
+
+    def local_set(self, set_idx):
+        return self.shared[self.rank, set_idx]
+
+
+def _fused_worker(rank, world, port, shared, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        slots = _SharedSlots(shared, rank)
+        log = []
+
+        def gemm_into(a_rows, b, target):
+            log.append(("gemm", int(a_rows.storage_offset() // a_rows.stride(0))))
+            target.copy_(O.reference_matmul(a_rows, b, None, torch.float32))
+
+        def reduce_fn(local_set, dst, bias):
+            acc = local_set[0].clone()
+            for s in range(1, local_set.shape[0]):
+                acc += local_set[s]
+            if bias is not None:
+                acc += bias.float()
+            dst.copy_(acc.to(dst.dtype))
+            log.append(("reduce",))
+
+        oks = []
+        for call in range(3):  # three calls: both slot sets are used and the first one is reused
+            case = O.Case("mgf", "bf16", "nt", 96, 256, 384, seed=90 + call, bias_std=0.5)
+            a, b, bias = O.draw_logical(case)
+            full = O.reference_matmul(a, b, bias, torch.bfloat16)
+            a_r, b_r, k0, k1 = MG.shard_along_k(a, b, world, rank)
+            res = MG.gemm_k_sharded_fused(a_r, b_r, torch.bfloat16, slots, bias=bias, layout="nt", gemm_into=gemm_into,
+                                          barrier=dist.barrier, reduce_fn=reduce_fn)
+            (r0, r1), = res.row_ranges
+            oks.append(bool(O.compare(res.out, full[r0:r1], case.k)["ok"]) and res.out.shape == (r1 - r0, 256))
+        ret[rank] = (all(oks), log[:world + 1], res.row_ranges, res.reduce_bytes, slots.calls)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_fused_send_order():
+    assert MG.fused_send_order(4, 1) == [2, 3, 0, 1]
+    assert MG.fused_send_order(1, 0) == [0]
+    for world in (2, 3, 8):  # at every step the ranks address distinct destinations
+        for step in range(world):
+            assert len({MG.fused_send_order(world, r)[step] for r in range(world)}) == world
+
+
+def test_three_rank_gloo_fused_k_shard():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    world, per, n = 3, 32, 256
+    shared = torch.full((world, 2, world, per, n), float("nan")).share_memory_()
+    ret = mp.Manager().dict()
+    mp.spawn(_fused_worker, args=(world, port, shared, ret), nprocs=world, join=True)
+    rows = set()
+    for r in range(world):
+        ok, log, ranges, reduce_bytes, calls = ret[r]
+        assert ok and calls == 3
+        # rows served in the order of the right-hand neighbours, own rows last, then the reduction
+        assert log == [("gemm", d * per) for d in MG.fused_send_order(world, r)] + [("reduce",)]
+        assert reduce_bytes == 4 * per * n * (world - 1)
+        rows |= set(range(*ranges[0]))
+    assert rows == set(range(world * per))
