@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the A16W16 GEMM hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4_nt|...|c5|c5_nshard|c5_kshard]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4_nt|...|c5|c5_nshard|c5_kshard|c5_kshard_fused]
                     [--impl ours|reference]
 
 Prints ONE JSON line. A step is one pass of the hot path (one GEMM call) over one batch of synthetic input.
@@ -186,7 +186,7 @@ class Workload:
 
         self.name, self.world, self.rank, self.device = name, world, rank, device
         self.extra = {}
-        big = name in ("c5", "c5_nshard", "c5_kshard")
+        big = name in ("c5", "c5_nshard", "c5_kshard", "c5_kshard_fused")
         self.case = case = O.CONFIGS["c5" if big else name]
         if args.policy:
             import dataclasses
@@ -198,21 +198,35 @@ class Workload:
             a_full = (torch.randn(case.m, case.k, device=device, dtype=torch.float32) * case.a_std).to(torch.bfloat16)
             self.rotation = "inputs larger than L2"
             self.total_flops = float(case.flops)
-            if name == "c5_kshard" and world > 1:
+            if name in ("c5_kshard", "c5_kshard_fused") and world > 1:
                 k0, k1 = MG.shard_bounds(case.k, world, rank, 64)
                 b_store = (torch.randn(case.n, k1 - k0, device=device, dtype=torch.float32) * case.b_std).to(torch.bfloat16)
                 a_loc, b_loc, chunks = a_full[:, k0:k1], b_store.t(), args.chunks
                 self.result = None
-
-                def step():
-                    self.result = MG.gemm_k_sharded(a_loc, b_loc, torch.bfloat16, layout="nt", chunks=chunks)
-
                 self.per_rank_flops = 2.0 * case.m * case.n * (k1 - k0)
-                self.plan = plan(a_loc[: case.m // chunks], b_loc, "nt", {}, out_dtype=torch.float32)
-                self.launches_per_step = 2 * chunks
-                self.gemm_launches_per_step = chunks
                 self.extra["reduce_bytes_per_rank"] = 4 * case.m * case.n * (world - 1) // world
-                self.partition = f"K sharded over {world} GPUs, NCCL fp32 reduce-scatter in {chunks} M-chunks"
+                if name == "c5_kshard":
+                    def step():
+                        self.result = MG.gemm_k_sharded(a_loc, b_loc, torch.bfloat16, layout="nt", chunks=chunks)
+
+                    self.plan = plan(a_loc[: case.m // chunks], b_loc, "nt", {}, out_dtype=torch.float32)
+                    self.launches_per_step = 2 * chunks
+                    self.gemm_launches_per_step = chunks
+                    self.partition = f"K sharded over {world} GPUs, NCCL fp32 reduce-scatter in {chunks} M-chunks"
+                else:
+                    per = case.m // world
+                    self.slots = MG.PeerSlots(per, case.n, device)
+                    out_loc = torch.empty((per, case.n), dtype=torch.bfloat16, device=device)
+
+                    def step():
+                        self.result = MG.gemm_k_sharded_fused(a_loc, b_loc, torch.bfloat16, self.slots, layout="nt",
+                                                              user_kwargs=case.user_kwargs, out=out_loc)
+
+                    self.plan = plan(a_loc[:per], b_loc, "nt", case.user_kwargs, out_dtype=torch.float32)
+                    self.launches_per_step = world + 1
+                    self.gemm_launches_per_step = world
+                    self.partition = (f"K sharded over {world} GPUs, GEMM epilogues store fp32 tiles into the owner's slots "
+                                      "over NVLink (peer memory), owner-side slot reduction")
                 ins = [a_loc, b_loc]
                 out_getter = lambda: self.result.out
             else:
@@ -292,7 +306,7 @@ class Workload:
         self.out_h = torch.empty(out0.shape, dtype=out0.dtype).pin_memory()
         self.h2d = sum(h.numel() * h.element_size() for h in self.host_in) + (0 if self.bias_h is None else self.bias_h.numel() * 2)
         self.d2h = self.out_h.numel() * self.out_h.element_size()
-        kshard = self.name == "c5_kshard" and self.world > 1
+        kshard = self.name in ("c5_kshard", "c5_kshard_fused") and self.world > 1
 
         # Three streams, two device copies of every buffer: the host->device copy of step i+1 and the device->host
         # read of step i-1 overlap the GEMM of step i (PCIe is full duplex). Every step still moves its own inputs in
@@ -329,7 +343,11 @@ class Workload:
             main.wait_event(ev_in[b])
             if i >= nbuf:
                 main.wait_event(ev_out[b])
-            if kshard:
+            if kshard and self.name == "c5_kshard_fused":
+                res = MG.gemm_k_sharded_fused(in_view[b][0], in_view[b][1], torch.bfloat16, self.slots, layout="nt",
+                                              user_kwargs=self._e2e_kwargs)
+                result = res.out
+            elif kshard:
                 res = MG.gemm_k_sharded(in_view[b][0], in_view[b][1], torch.bfloat16, layout="nt", chunks=self.plan_chunks)
                 result = res.out
             else:
@@ -478,7 +496,7 @@ def run_ours(args) -> dict:
         "warmup": args.warmup,
         "ms_per_step": ms_per_step,
         "higher_is_better": True,
-        "scaling": "strong" if workload in ("c5_nshard", "c5_kshard") else "weak",
+        "scaling": "strong" if workload in ("c5_nshard", "c5_kshard", "c5_kshard_fused") else "weak",
         "vs_baseline": None,
         "dtype": case.dtype,
         "data": "synthetic",
@@ -553,7 +571,7 @@ def run_reference(args) -> dict | None:
         "warmup": args.warmup,
         "ms_per_step": statistics.median(r["full_pass_seconds_est"] for r in runs) * 1e3,
         "higher_is_better": True,
-        "scaling": "strong" if workload in ("c5_nshard", "c5_kshard") else "weak",
+        "scaling": "strong" if workload in ("c5_nshard", "c5_kshard", "c5_kshard_fused") else "weak",
         "vs_baseline": None,
         "dtype": case.dtype,
         "data": "synthetic",
