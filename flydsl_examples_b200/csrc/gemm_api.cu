@@ -257,6 +257,10 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
     pl.num_units = (int)(tiles * s);
     pl.grid = pl.num_units;
     pl.cluster_split = s > 1 ? s : 0;
+    // Tiles wider than 64 receive the cluster's rows (128 x tile_n floats) in the operand ring: it must be that large.
+    if (pl.cluster_split && pl.tile_n > 64 &&
+        pl.stages * (kTileP * pl.tile_k * 2 + pl.tile_n * pl.tile_k * 2) < kTileP * pl.tile_n * 4)
+      return B200_GEMM_ERR_BAD_POLICY;
   }
   const bool tickets = (pl.split_k > 1 && pl.cluster_split == 0) || pl.sk_tiles > 0;
   if (tickets && tiles * pl.cta_group > (int64_t)(kCounterBytes / 4)) return B200_GEMM_ERR_TOO_LARGE;

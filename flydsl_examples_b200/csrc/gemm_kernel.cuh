@@ -63,10 +63,10 @@ struct alignas(64) GemmParams {
   uint32_t u_kstep, v_kstep;  // start-address increment (16-byte units) per K=16 MMA inside a stage
 };
 
-// One piece of work of a CTA: K blocks [kb0, kb0+kbn) of output tile (tp, tq). When `partial`, the fp32 result goes to
+// One piece of work of a CTA: K blocks kb0, kb0+kstep, ... (kbn of them) of output tile (tp, tq). When `partial`, the fp32 result goes to
 // slot `slot` of the workspace and the last of `n_contrib` contributors (ticket) reduces slots slot0..slot0+n_contrib-1.
 struct Unit {
-  int tile, tp, tq, kb0, kbn;
+  int tile, tp, tq, kb0, kbn, kstep;
   int partial, slot, slot0, n_contrib;
 };
 
@@ -109,6 +109,7 @@ struct WorkIter {
       w.tile = (int)(sk_cur / p.kb_total);
       w.kb0 = (int)(sk_cur - (long long)w.tile * p.kb_total);
       w.kbn = (int)min((long long)(p.kb_total - w.kb0), sk_end - sk_cur);
+      w.kstep = 1;
       sk_cur += w.kbn;
       raster_tile(p, w.tile, w.tp, w.tq);
       w.partial = w.kbn != p.kb_total;
@@ -126,7 +127,7 @@ struct WorkIter {
       w.tile = next_u;
       next_u += count;
       raster_tile(p, w.tile, w.tp, w.tq);
-      w.kb0 = 0, w.kbn = p.kb_total, w.partial = 0;
+      w.kb0 = 0, w.kbn = p.kb_total, w.kstep = 1, w.partial = 0;
       return true;
     }
     if (next_u >= p.num_units) return false;
@@ -135,9 +136,12 @@ struct WorkIter {
     w.tile = u / p.split_k;
     const int slice = u - w.tile * p.split_k;
     raster_tile(p, w.tile, w.tp, w.tq);
-    const int base = p.kb_total / p.split_k, rem = p.kb_total - base * p.split_k;
-    w.kb0 = slice * base + min(slice, rem);
-    w.kbn = base + (slice < rem ? 1 : 0);
+    // Slice s takes K blocks s, s + split_k, ...: the slices of a tile run at the same time on neighbouring CTAs, so
+    // together they read split_k consecutive 128-byte pieces of every operand row at about the same moment, which
+    // DRAM serves from one open page; contiguous K ranges per slice would touch each page split_k separate times.
+    w.kb0 = slice;
+    w.kstep = p.split_k;
+    w.kbn = (p.kb_total - slice + p.split_k - 1) / p.split_k;
     w.partial = p.split_k > 1;
     w.n_contrib = p.split_k;
     w.slot0 = w.tile * p.split_k;
@@ -362,7 +366,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         const int u = w.tile;
         const int p0 = (w.tp * CG + rank) * kTileP, q0 = w.tq * TILE_Q + rank * kVRows;
         if (lane == 0) trace_stamp(p, 0, item, 0);
-        for (int kb = w.kb0; kb < w.kb0 + w.kbn; ++kb) {
+        for (int kj = 0; kj < w.kbn; ++kj) {
+          const int kb = w.kb0 + kj * w.kstep;
           if (issued >= STAGES) {
             int good = 1;
             if (lane == 0) good = mbar_wait<CG == 2>(empty_bar(stage), phase ^ 1u, abort_s) ? 1 : 0;
@@ -373,7 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
               break;
             }
           }
-          if (kb == w.kb0 && lane == 0) trace_stamp(p, 0, item, 1);
+          if (kj == 0 && lane == 0) trace_stamp(p, 0, item, 1);
           // Data of both CTAs of a pair is counted on the leader's barrier, which the MMA thread waits on.
           uint32_t fb = full_bar(stage);
           if constexpr (CG == 2) fb = mapa_cluster(fb, 0);
@@ -607,7 +612,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
             mbar_arrive(acce_bar(buf));
         }
       };
-      uint32_t cl_dst = 0, cl_swz = 0;
+      uint32_t cl_stage = 0;
       if (cluster_mode) {
         if (cluster_wait_due) {
           cluster_wait();
@@ -618,11 +623,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
           cluster_wait();
           ring_idle_barrier_due = false;
         }
-        const int rows_per_cta = kTileP / p.cluster_split;
-        const uint32_t local = base + L::kRecvOff +
-                               (uint32_t)(((int)cluster_ctarank() * rows_per_cta + row % rows_per_cta) * TILE_Q) * 4u;
-        cl_dst = mapa_cluster(local, (uint32_t)(row / rows_per_cta));
-        cl_swz = (uint32_t)((row % rows_per_cta) & 7) & (uint32_t)(TILE_Q / 4 - 1);
+        // Scatter staging: 32 rows x CW floats per epilogue warp. Wide tiles use the TMA-store staging area (unused in
+        // this mode); narrower ones the head of this CTA's own ring, idle now that its accumulator is complete.
+        cl_stage = base + (L::kRecvInRing ? L::kOutOff : 0) + (uint32_t)(warp - 2) * (32u * CW * 4u);
       }
       // TMA-store path: bias + cast, then this lane's row segment goes into the warp's swizzled staging image
       // (16-byte chunk j of row t sits at position j ^ (t % 8)); every full 128-byte row image is stored by one lane.
@@ -696,16 +699,38 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         } else if (direct) {
           finalize_chunk<CW>(p, v, prow, qbase + c * CW, bias_s + c * CW, bias_p);
         } else if (cluster_mode) {
-          // cluster split-K: this row's partial sums go to the CTA that owns the row, into slab [my rank][row % R].
-          // 16-byte chunk g of a row is stored at position g ^ (row % 8) (capped to the chunks a row has), so that the
-          // 32 lanes of a warp, which write 32 different rows, spread over all banks of the receiver.
+          // cluster split-K: the partial sums of row r go to the CTA that owns r, into its image
+          // recv[source rank][chunk][r % R][CW]. A lane holds one row, so the warp first transposes through its staging
+          // image (16-byte piece j of row t at position j ^ (t % 8), conflict-free) and then copies it out with every
+          // warp-wide store covering whole 128-byte rows: remote shared-memory stores are only fast when coalesced.
+          constexpr int kPieces = CW / 4;             // 16-byte pieces per row of a chunk
+          constexpr int kRowsPerStep = 32 / kPieces;  // rows one warp-wide store covers
+          const uint32_t my_row = cl_stage + (uint32_t)lane * (CW * 4u);
 #pragma unroll
-          for (int j = 0; j < CW / 4; ++j) {
-            const uint32_t g = (uint32_t)(c * (CW / 4) + j) ^ cl_swz;
-            asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cl_dst + g * 16u), "f"(v[4 * j]), "f"(v[4 * j + 1]),
-                         "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+          for (int j = 0; j < kPieces; ++j) {
+            const uint32_t addr = my_row + (uint32_t)((j ^ (lane & (kPieces - 1))) << 4);
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]),
+                         "f"(v[4 * j + 3])
                          : "memory");
           }
+          __syncwarp();
+          const int R = kTileP / p.cluster_split;
+          const uint32_t recv_chunk = base + L::kRecvOff + (uint32_t)(((int)cluster_ctarank() * NCHUNK + c) * R) * (CW * 4u);
+#pragma unroll
+          for (int step = 0; step < kPieces; ++step) {
+            const int t = step * kRowsPerStep + lane / kPieces;  // row inside this warp's 32
+            const uint32_t piece = (uint32_t)(lane % kPieces) << 4;
+            float4 x;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
+                         : "r"(cl_stage + (uint32_t)t * (CW * 4u) + piece)
+                         : "memory");
+            const int trow = quarter * 32 + t;
+            const uint32_t dst = mapa_cluster(recv_chunk + (uint32_t)(trow % R) * (CW * 4u) + piece, (uint32_t)(trow / R));
+            asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w)
+                         : "memory");
+          }
+          __syncwarp();  // the staging image is rewritten by the next chunk
         } else {
           // slot layout [chunk][4-column group][row][4]: one warp store covers 512 contiguous bytes
           float4* dst = part + (size_t)c * (CW / 4) * kTileP;
@@ -834,7 +859,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
             reinterpret_cast<__half*>(p.out)[idx] = __float2half_rn(acc);
         }
       };
-      constexpr uint32_t kSwzMask = TILE_Q / 4 - 1;  // TILE_Q / 4 chunks per row (a power of two)
+      constexpr int kPieces = CW / 4;  // 16-byte pieces per row of a chunk; piece j of row t sits at j ^ (t % kPieces)
       if (!p.swap_out) {
         // four consecutive columns per thread and step: float4 reads of the slabs, bias from the staged slice,
         // one 8- or 16-byte store (scalar stores at ragged edges or unaligned rows)
@@ -842,10 +867,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
 #pragma unroll 2
         for (int e = et; e < R * (TILE_Q / 4); e += kEpiThreads) {
           const int lrow = e / (TILE_Q / 4), g = e % (TILE_Q / 4), col = g * 4;
-          const int gs = (int)((uint32_t)g ^ ((uint32_t)(lrow & 7) & kSwzMask));
+          const int off = ((g / kPieces) * R + lrow) * CW + (((g % kPieces) ^ (lrow & (kPieces - 1))) << 2);
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
           for (int src = 0; src < S; ++src) {
-            const float4 x = *reinterpret_cast<const float4*>(recv + (src * R + lrow) * TILE_Q + gs * 4);
+            const float4 x = *reinterpret_cast<const float4*>(recv + src * (R * TILE_Q) + off);
             acc.x += x.x, acc.y += x.y, acc.z += x.z, acc.w += x.w;
           }
           const int prow = tp * kTileP + crank * R + lrow, q = tq * TILE_Q + col;
@@ -881,10 +906,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         // D^T output: consecutive threads take consecutive rows, which are contiguous in memory
 #pragma unroll 4
         for (int e = et; e < R * TILE_Q; e += kEpiThreads) {
-          const int lrow = e % R, col = e / R;
-          const int off = (int)((((uint32_t)(col >> 2)) ^ ((uint32_t)(lrow & 7) & kSwzMask)) * 4u) + (col & 3);
+          const int lrow = e % R, col = e / R, g = col >> 2;
+          const int off = ((g / kPieces) * R + lrow) * CW + (((g % kPieces) ^ (lrow & (kPieces - 1))) << 2) + (col & 3);
           float acc = 0.f;
-          for (int src = 0; src < S; ++src) acc += recv[(src * R + lrow) * TILE_Q + off];
+          for (int src = 0; src < S; ++src) acc += recv[src * (R * TILE_Q) + off];
           emit(acc, tp * kTileP + crank * R + lrow, tq * TILE_Q + col);
         }
       }

@@ -169,6 +169,12 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
         return f"group_m must be >= 0, got {pol.group_m}"
     if pol.split_mode == "cluster" and pol.split_k > 1 and (pol.cta_group != 1 or pol.stream_k):
         return "cluster split-K needs cta_group 1 and no stream_k"
+    if pol.split_mode == "cluster" and pol.split_k > 1 and pol.tile_n > 64:
+        # wide tiles receive the cluster's rows (128 x tile_n floats) in the operand ring
+        tk = tile_k(pol.tile_n, 1, pol.tile_k)
+        stages = min(pol.stages or 99, max_stages(pol.tile_n, 1, pol.tile_k))
+        if stages * (TILE_M + pol.tile_n) * tk * 2 < TILE_M * pol.tile_n * 4:
+            return f"cluster split-K with tile_n {pol.tile_n} needs a ring of at least {TILE_M * pol.tile_n * 4} bytes"
     # The operand on the MMA N axis, when it is contiguous along N (or M after a swap), is fetched as 64-wide boxes.
     a_mn = layout[0] == "t"
     b_mn = layout[1] == "n"
