@@ -104,6 +104,11 @@ struct WorkIter {
   __device__ __forceinline__ int owner(long long x) const {
     return (int)(((x + 1) * count + sk_total - 1) / sk_total) - 1;
   }
+  // After next(): does this walker have another unit to come?
+  __device__ __forceinline__ bool more(const GemmParams& p) const {
+    if (sk_cur < sk_end) return true;
+    return next_u < (p.sk_tiles > 0 ? p.num_tiles : p.num_units);
+  }
   __device__ __forceinline__ bool next(const GemmParams& p, Unit& w) {
     if (sk_cur < sk_end) {
       w.tile = (int)(sk_cur / p.kb_total);
@@ -137,8 +142,7 @@ struct WorkIter {
     const int slice = u - w.tile * p.split_k;
     raster_tile(p, w.tile, w.tp, w.tq);
     // Slice s takes K blocks s, s + split_k, ...: the slices of a tile run at the same time on neighbouring CTAs, so
-    // together they read split_k consecutive 128-byte pieces of every operand row at about the same moment, which
-    // DRAM serves from one open page; contiguous K ranges per slice would touch each page split_k separate times.
+    // together they walk every operand row front to back instead of starting at split_k distant offsets.
     w.kb0 = slice;
     w.kstep = p.split_k;
     w.kbn = (p.kb_total - slice + p.split_k - 1) / p.split_k;
@@ -630,7 +634,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       // TMA-store path: bias + cast, then this lane's row segment goes into the warp's swizzled staging image
       // (16-byte chunk j of row t sits at position j ^ (t % 8)); every full 128-byte row image is stored by one lane.
       const bool staged = direct && p.tma_store != 0 && TILE_Q >= 64;
-      const uint32_t out_stage0 = base + L::kOutOff + (uint32_t)(warp - 2) * (2 * L::kStageOutBytes);
+      // The warp normally alternates between two 4 KB staging images and waits for the TMA store that last read one
+      // before rewriting it. In a CTA's last work item nothing will be loaded into the operand ring any more and the
+      // accumulator being complete means the ring has been read: every flush then gets an image of its own in the ring
+      // and never waits (the exposed epilogue at the end of the kernel is otherwise bound by TMA-store round trips).
+      constexpr int kFlushesPerTile = NCHUNK;  // at most one flush per chunk (fp32 output)
+      const bool tail_stage = L::kRingBytes >= 4 * kFlushesPerTile * L::kStageOutBytes && !wi.more(p);
+      const uint32_t out_stage0 = tail_stage ? base + (uint32_t)(warp - 2) * (uint32_t)(kFlushesPerTile * L::kStageOutBytes)
+                                             : base + L::kOutOff + (uint32_t)(warp - 2) * (2 * L::kStageOutBytes);
+      if (tail_stage) out_flip = 0;
+      auto stage_image = [&]() -> uint32_t {
+        return out_stage0 + (uint32_t)(tail_stage ? out_flip : (out_flip & 1)) * L::kStageOutBytes;
+      };
       auto stage_flush = [&](int col0) {
         fence_proxy_async_smem();
         __syncwarp();
@@ -638,13 +653,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         if (lane == 0) {
           // a box that starts outside C holds nothing to write; one that straddles the edge is clipped by TMA
           if (row0 < p.P && col0 < p.Q)
-            tma_store_2d(&p.tmap_out, col0, row0, out_stage0 + (uint32_t)(out_flip & 1) * L::kStageOutBytes);
+            tma_store_2d(&p.tmap_out, col0, row0, stage_image());
           tma_store_commit();
         }
         ++out_flip;
       };
       auto stage_acquire = [&]() {
         // the store issued two flushes ago has finished reading the buffer about to be overwritten
+        if (tail_stage) return;  // every flush of a CTA's last work item has its own image
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
       };
@@ -655,10 +671,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         if (staged) {
           if constexpr (CW == 32) {
             if (p.bias != nullptr) {
+              const float4* b4 = reinterpret_cast<const float4*>(bias_s + c * CW);  // 16-byte aligned: one load per 4 columns
 #pragma unroll
-              for (int i = 0; i < CW; ++i) v[i] += bias_s[c * CW + i];
+              for (int j = 0; j < CW / 4; ++j) {
+                const float4 b = b4[j];
+                v[4 * j] += b.x, v[4 * j + 1] += b.y, v[4 * j + 2] += b.z, v[4 * j + 3] += b.w;
+              }
             }
-            const uint32_t row_base = out_stage0 + (uint32_t)(out_flip & 1) * L::kStageOutBytes + (uint32_t)lane * 128u;
+            const uint32_t row_base = stage_image() + (uint32_t)lane * 128u;
             if (p.out_dtype == 1) {
               stage_acquire();
 #pragma unroll
