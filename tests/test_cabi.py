@@ -58,3 +58,32 @@ def test_bad_arguments_return_codes_not_crashes():
     assert lib.b200_gemm_plan_query(C.byref(args), C.byref(pl)) == -1
     assert lib.b200_gemm_workspace_bytes(C.byref(args)) == 0
     assert lib.b200_gemm_plan_query(None, C.byref(pl)) == -1
+
+
+def test_multi_gpu_entry_points_validate_before_touching_a_device():
+    lib = _lib.load()
+    h = _lib.PeerHandle()
+    assert C.sizeof(_lib.PeerHandle) == 88  # 64-byte IPC handle + offset + bytes + device + reserved
+    ptr = C.c_void_p()
+    assert lib.b200_peer_export(None, C.byref(h)) == -1
+    assert lib.b200_peer_export(C.c_void_p(4096), None) == -1
+    assert lib.b200_peer_open(None, C.byref(ptr)) == -1
+    assert lib.b200_peer_open(C.byref(h), None) == -1
+    assert lib.b200_peer_close(None, C.byref(h)) == -1
+    # reduce_slots: null pointers, no slots, cols not a multiple of 4, slots closer together than one image,
+    # misaligned base, unknown dtype: all refused with BAD_ARG, nothing launched
+    ok = (C.c_void_p(4096), 1024, 2, C.c_void_p(8192), None, 4, 256, 2, 0, None)
+    def call(**kw):
+        names = ("slots", "stride", "n", "out", "bias", "rows", "cols", "odt", "bdt", "stream")
+        vals = dict(zip(names, ok))
+        vals.update(kw)
+        return lib.b200_gemm_reduce_slots(*[vals[k] for k in names])
+    assert call(slots=None) == -1 and call(out=None) == -1
+    assert call(n=0) == -1
+    assert call(cols=254) == -1
+    assert call(stride=512) == -1          # two 4x256 images cannot be 512 elements apart
+    assert call(stride=1026) == -1         # not a multiple of 4 elements
+    assert call(slots=C.c_void_p(4100)) == -1
+    assert call(odt=7) == -1
+    assert call(bias=C.c_void_p(64), bdt=1) == -1  # bias must be bf16 or fp16
+    assert call(rows=0) == 0               # nothing to do is not an error
