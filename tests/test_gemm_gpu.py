@@ -215,6 +215,57 @@ def test_split_k_shapes(layout, dtype, idx):
                  repeats=2, prefill="randn")
 
 
+# The reference's benchmark list with the reference's own policy dicts (test_gemm_a16w16_gfx950.py:628-649): the
+# gfx950 wave/tile keys are accepted and ignored, group_m carries over, the tiling comes from the shipped table or the
+# heuristic. Shapes whose full fp32 CPU product would take minutes are checked on sampled full rows and columns.
+REFERENCE_BENCH = [  # m, n, k, block_m, block_n, block_k, stages, m_waves, n_waves, group_m, hti
+    (8, 4096, 4096, 16, 16, 128, 8, 1, 1, 4, False),
+    (16, 4096, 4096, 16, 16, 128, 8, 1, 1, 4, False),
+    (32, 4096, 4096, 16, 16, 64, 8, 1, 1, 0, False),
+    (64, 4096, 4096, 32, 32, 64, 8, 2, 2, 4, False),
+    (128, 4096, 4096, 64, 32, 128, 4, 4, 2, 4, False),
+    (256, 4096, 4096, 64, 64, 64, 7, 4, 2, 4, False),
+    (512, 4096, 4096, 64, 128, 64, 6, 2, 4, 4, False),
+    (1024, 4096, 4096, 128, 128, 64, 4, 2, 4, 4, False),
+    (2048, 4096, 4096, 128, 256, 64, 3, 4, 4, 4, False),
+    (1024, 1024, 1024, 64, 64, 64, 4, 2, 4, 0, False),
+    (2048, 2048, 2048, 128, 128, 64, 3, 4, 2, 0, False),
+    (4096, 4096, 4096, 256, 256, 64, 2, 2, 4, 4, True),
+    (4096, 4096, 8192, 256, 256, 64, 2, 2, 4, 4, True),
+    (8192, 8192, 8192, 256, 256, 64, 2, 2, 4, 0, True),
+    (8, 7168, 2048, 16, 16, 128, 8, 1, 1, 4, False),
+    (32, 384, 7168, 16, 16, 128, 8, 1, 1, 0, False),
+    (32, 14336, 4096, 32, 64, 64, 8, 2, 2, 0, False),
+    (16, 28672, 4096, 16, 64, 128, 3, 1, 4, 4, False),
+    (4096, 256, 4096, 64, 64, 64, 6, 4, 2, 4, False),
+]
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("idx", range(len(REFERENCE_BENCH)))
+def test_reference_bench_list_with_reference_policies(dtype, idx):
+    m, n, k, bm, bn, bk, stages, mw, nw, gm, hti = REFERENCE_BENCH[idx]
+    kw = {"block_m": bm, "block_n": bn, "block_k": bk, "stages": stages, "m_waves": mw, "n_waves": nw, "group_m": gm,
+          "use_half_tile_interleaved": hti}
+    big = m * n * k > 1 << 34
+    if big and dtype == "fp16":
+        pytest.skip("the large shapes run once (bf16): their CPU check dominates the test time")
+    layouts = ("nt",) if big else (("nt", "nn") if m * n * k > 1 << 31 else LAYOUTS)
+    for layout in layouts:
+        if (layout[0] == "t" and m % 8) or (layout[1] == "n" and n % 8):
+            continue
+        case = O.Case("refbench", dtype, layout, m, n, k, seed=600 + idx, bias_std=0.5, user_kwargs=kw)
+        if not big:
+            run_case(case)
+            continue
+        a, b, bias, a_l, b_l, bias_l = O.build_inputs(case, device=DEV)
+        out = torch.full((m, n), float("nan"), dtype=case.torch_out_dtype, device=DEV)
+        got = gemm_a16w16(a, b, out, bias=bias, user_kwargs=kw, layout=layout)
+        check_status()
+        assert bool(torch.isfinite(got).all())
+        sampled_check(got, a_l, b_l, bias_l, k, case.torch_out_dtype, n_rows=24, n_cols=24, seed=idx)
+
+
 PAIR = [  # a CTA pair per 256-row tile (tcgen05 cta_group::2)
     (256, 256, 64, {"tile_n": 256, "cta_group": 2}),
     (1024, 1024, 512, {"tile_n": 256, "cta_group": 2}),
