@@ -67,7 +67,7 @@ constexpr KernelFn kfn() {
     return nullptr;
 }
 
-// Stages of 64 K elements: wide tiles and CTA pairs. Stages of 128 K elements: narrow single-CTA tiles.
+// Stages of 64 K elements: every tile and CTA pair. Stages of 128 K elements: single-CTA tiles up to 128 wide (default there).
 #define B200_VARIANT_K64(TQ, CG, MAXS)                                                                            \
   {                                                                                                               \
     TQ, CG, 64, MAXS, {                                                                                           \
