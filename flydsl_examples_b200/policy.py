@@ -186,11 +186,11 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
     return None
 
 
-# Rough cost of one 64-deep K block of a tile, in SM cycles, used only to rank candidate tilings. The tensor pipe
-# needs 128 cycles per 128 x 256 x 16 MMA; one thread issues them and pays a fixed price per K block (barrier poll,
-# four MMAs, commit), which is what bounds narrow tiles; the fed fraction comes from ncu on large GEMMs
-# (0.72 with one CTA per tile, 0.87 with a CTA pair).
-_KBLOCK_CYCLES = {(1, 256): 512 / 0.72, (2, 256): 512 / 0.87, (1, 128): 340.0, (1, 64): 300.0, (1, 32): 310.0, (1, 16): 320.0}
+# Rough cost of one 64-deep K block of a tile, in SM cycles, used only to rank candidate tilings. Two bounds, both
+# measured: the tensor pipe needs 128 cycles per 128 x 256 x 16 MMA, and one SM takes in about 64 bytes per clock
+# from L2, i.e. 2 * (128 + tile_n) cycles for the 128 + tile_n operand rows of a block (a CTA of a pair loads half of
+# the tile_n rows). Every single-CTA tile is bound by the second; the 256 x 256 pair balances the two.
+_KBLOCK_CYCLES = {(1, 256): 800.0, (2, 256): 590.0, (1, 128): 540.0, (1, 64): 400.0, (1, 32): 340.0, (1, 16): 310.0}
 _FIXED_CYCLES = 6000.0  # launch tail, pipeline fill, last epilogue
 
 
@@ -211,10 +211,13 @@ def _auto_split(tiles: int, kb: int, walkers: int, cluster_ok: bool = False) -> 
 def _estimate_cycles(p_ext: int, q: int, kb: int, cta_group: int, tile_n: int, num_sms: int) -> float:
     walkers = max(1, num_sms // cta_group)
     tiles = -(-p_ext // (TILE_M * cta_group)) * -(-q // tile_n)
-    split, _ = _auto_split(tiles, kb, walkers, cta_group == 1)
+    split, _ = _auto_split(tiles, kb, walkers, cta_group == 1 and tile_n <= 64)
     waves = -(-(tiles * split) // walkers)
     epilogue = 1000.0 + 500.0 * tile_n / 256
-    fixup = (1500.0 + 400.0 * split) if split > 1 else 0.0
+    # after the main loop: a cluster exchange of a narrow tile costs about 1 us, a reduction through global memory
+    # (partial write, fences and ticket, read-back) about 5 us
+    # (the last arriver reads split slabs of 128 x tile_n floats at about 24 bytes per clock)
+    fixup = 0.0 if split <= 1 else (1500.0 + 200.0 * split) if (cta_group == 1 and tile_n <= 64) else (8000.0 + 21.0 * split * tile_n)
     return _FIXED_CYCLES + waves * (-(-kb // split) * _KBLOCK_CYCLES[(cta_group, tile_n)] + epilogue) + fixup
 
 
@@ -240,7 +243,7 @@ def heuristic(m: int, n: int, k: int, layout: str = "nt", num_sms: int = NUM_SMS
         cta_group, tile_n = best
     walkers = num_sms // cta_group
     tiles = -(-p_ext // (TILE_M * cta_group)) * -(-q // tile_n)
-    split, mode = _auto_split(tiles, kb, walkers, cta_group == 1)
+    split, mode = _auto_split(tiles, kb, walkers, cta_group == 1 and tile_n <= 64)
     group = 8 if (tiles >= 2 * walkers and not swap) else 0
     return Policy(tile_n=tile_n, split_k=split, group_m=group, swap_ab=swap, cta_group=cta_group, split_mode=mode)
 
