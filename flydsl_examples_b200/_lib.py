@@ -118,6 +118,7 @@ EXPORTS = (
     "b200_peer_export",
     "b200_peer_open",
     "b200_peer_close",
+    "b200_gemm_selftest",
     "b200_gemm_strerror",
     "b200_gemm_version",
 )
@@ -177,6 +178,8 @@ def load() -> C.CDLL:
     lib.b200_peer_open.restype = C.c_int
     lib.b200_peer_close.argtypes = [C.c_void_p, C.POINTER(PeerHandle)]
     lib.b200_peer_close.restype = C.c_int
+    lib.b200_gemm_selftest.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
+    lib.b200_gemm_selftest.restype = C.c_int
     lib.b200_gemm_strerror.argtypes = [C.c_int]
     lib.b200_gemm_strerror.restype = C.c_char_p
     lib.b200_gemm_version.argtypes = []

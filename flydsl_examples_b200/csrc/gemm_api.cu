@@ -561,6 +561,85 @@ int b200_gemm_a16w16_static_scratch(const b200_gemm_args* args, void* cuda_strea
   return b200::run(&h, stream);
 }
 
+int b200_gemm_selftest(void* cuda_stream, int32_t* failed_case) {
+  // Scratch map (bytes from the start of the built-in array): GEMM workspace | A | B | bias | out | reference | counters.
+  constexpr size_t kWs = 0, kWsBytes = 8u << 20, kA = kWsBytes, kB = kA + (512u << 10), kBias = kB + (512u << 10),
+                   kOut = kBias + (64u << 10), kRef = kOut + (512u << 10), kFlag = kRef + (512u << 10);
+  static_assert(kFlag + 256 <= (size_t)B200_GEMM_STATIC_SCRATCH_BYTES, "self-test scratch map");
+  constexpr int M = 200, N = 264, K = 328;  // ragged against every tile; all pitches are multiples of 16 bytes
+  struct Case {
+    int tile_n, cta_group, split_k, split_mode, stream_k, swap_ab, tile_k, fp32_out, bias, k_major_only;
+  };
+  static const Case cases[] = {
+      {64, 1, 1, 0, 0, 0, 0, 0, 1, 0},  {128, 1, 1, 0, 0, 0, 0, 1, 0, 0},  {256, 1, 1, 0, 0, 0, 0, 0, 1, 0},
+      {128, 2, 1, 0, 0, 0, 0, 0, 1, 0}, {256, 2, 1, 0, 0, 0, 0, 1, 1, 0},  {128, 1, 1, 0, 0, 0, 64, 0, 0, 0},
+      {64, 1, 3, 0, 0, 0, 0, 1, 1, 0},  {64, 1, 2, 2, 0, 0, 0, 0, 1, 0},   {128, 1, 1, 0, 1, 0, 0, 0, 1, 0},
+      {16, 1, 1, 0, 0, 0, 0, 0, 1, 1},  {32, 1, 2, 2, 0, 0, 64, 1, 0, 1},  {16, 1, 4, 2, 0, 1, 0, 1, 1, 1},
+  };
+  if (failed_case) *failed_case = -1;
+  void* scratch_v = nullptr;
+  int rc = b200::static_scratch_for_current_device(&scratch_v);
+  if (rc) return rc;
+  unsigned char* scratch = static_cast<unsigned char*>(scratch_v);
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+  int* flag = reinterpret_cast<int*>(scratch + kFlag);
+  int index = 0;
+  for (int dtype = 2; dtype <= 3; ++dtype) {
+    for (int layout = 0; layout < 4; ++layout) {
+      const int a_trans = layout >> 1, b_trans = layout & 1;
+      uint16_t* a = reinterpret_cast<uint16_t*>(scratch + kA);
+      uint16_t* b = reinterpret_cast<uint16_t*>(scratch + kB);
+      uint16_t* bias = reinterpret_cast<uint16_t*>(scratch + kBias);
+      const int a_rows = a_trans ? K : M, a_cols = a_trans ? M : K;
+      const int b_rows = b_trans ? N : K, b_cols = b_trans ? K : N;
+      b200::selftest_fill_kernel<<<64, 256, 0, stream>>>(a, a_rows, a_cols, a_cols, dtype, 1 + layout);
+      b200::selftest_fill_kernel<<<64, 256, 0, stream>>>(b, b_rows, b_cols, b_cols, dtype, 2 + dtype);
+      b200::selftest_fill_kernel<<<1, 256, 0, stream>>>(bias, 1, N, N, dtype, 3);
+      for (int with_bias = 0; with_bias < 2; ++with_bias)
+        b200::selftest_ref_kernel<<<128, 256, 0, stream>>>(a, a_cols, a_trans, b, b_cols, b_trans, with_bias ? bias : nullptr, M,
+                                                           N, K, dtype,
+                                                           reinterpret_cast<float*>(scratch + kRef) + (size_t)with_bias * M * N);
+      for (const Case& c : cases) {
+        ++index;
+        // The operand on the MMA N axis of a tile narrower than 64 must be K-contiguous: B stored [N,K], or A [M,K] after a swap.
+        if (c.k_major_only && (c.swap_ab ? a_trans != 0 : b_trans == 0)) continue;
+        b200_gemm_args args;
+        memset(&args, 0, sizeof(args));
+        args.a = a, args.b = b, args.out = scratch + kOut, args.bias = c.bias ? bias : nullptr;
+        args.m = M, args.n = N, args.k = K;
+        args.lda = a_cols, args.ldb = b_cols, args.ldo = N;
+        args.a_trans = a_trans, args.b_trans = b_trans;
+        args.in_dtype = dtype, args.out_dtype = c.fp32_out ? B200_GEMM_DTYPE_FP32 : dtype;
+        args.policy.tile_n = c.tile_n, args.policy.cta_group = c.cta_group, args.policy.split_k = c.split_k;
+        args.policy.split_mode = c.split_mode, args.policy.stream_k = c.stream_k, args.policy.swap_ab = c.swap_ab;
+        args.policy.tile_k = c.tile_k;
+        args.workspace = scratch + kWs, args.workspace_bytes = kWsBytes;
+        cudaError_t e = cudaMemsetAsync(scratch + kWs, 0, B200_GEMM_COUNTER_BYTES, stream);  // tickets start at zero
+        if (e == cudaSuccess) e = cudaMemsetAsync(scratch + kOut, 0xff, (size_t)M * N * 4, stream);  // NaN-poison the output
+        if (e == cudaSuccess) e = cudaMemsetAsync(flag, 0, sizeof(int), stream);
+        if (e != cudaSuccess) return b200::set_cuda_error(e);
+        rc = b200_gemm_a16w16(&args, cuda_stream);
+        if (rc) {
+          if (failed_case) *failed_case = index;
+          return rc;
+        }
+        b200::selftest_compare_kernel<<<64, 256, 0, stream>>>(scratch + kOut, args.out_dtype,
+                                                             reinterpret_cast<float*>(scratch + kRef) + (size_t)(c.bias ? 1 : 0) * M * N,
+                                                             (long long)M * N, flag);
+        int bad = 0;
+        e = cudaMemcpyAsync(&bad, flag, sizeof(int), cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+        if (e != cudaSuccess) return b200::set_cuda_error(e);
+        if (bad != 0) {
+          if (failed_case) *failed_case = index;
+          return B200_GEMM_ERR_SELFTEST;
+        }
+      }
+    }
+  }
+  return B200_GEMM_OK;
+}
+
 int b200_gemm_a16w16(const b200_gemm_args* args, void* cuda_stream) {
   b200_gemm_handle h;
   const int rc = b200::prepare(args, &h);
@@ -708,6 +787,7 @@ const char* b200_gemm_strerror(int code) {
     case B200_GEMM_ERR_LAUNCH: return b200::g_last_cuda_error[0] ? b200::g_last_cuda_error : "CUDA runtime error";
     case B200_GEMM_ERR_DRIVER: return "a CUDA driver entry point (cuTensorMapEncodeTiled, cuMemGetAddressRange) is not available";
     case B200_GEMM_ERR_TOO_LARGE: return "size beyond a fixed limit of this entry point";
+    case B200_GEMM_ERR_SELFTEST: return "self-test: a known-answer case gave a wrong result";
     default: return "unknown error code";
   }
 }

@@ -1041,4 +1041,57 @@ __global__ void reduce_slots_kernel(const float* __restrict__ slots, long long s
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Self-test helpers (b200_gemm_selftest): small-integer operands, an exact CUDA-core reference, an exact compare.
+__device__ __forceinline__ uint16_t selftest_encode_float(float v, int dtype) {
+  if (dtype == 2) {
+    __nv_bfloat16 h = __float2bfloat16_rn(v);
+    return *reinterpret_cast<uint16_t*>(&h);
+  }
+  __half h = __float2half_rn(v);
+  return *reinterpret_cast<uint16_t*>(&h);
+}
+__device__ __forceinline__ uint16_t selftest_encode(int v, int dtype) { return selftest_encode_float((float)v, dtype); }
+
+// dst[r * ld + c] = ((r * 131 + c * 71 + seed) % 5) - 2 for r < rows, c < cols, as bf16 / fp16.
+__global__ void selftest_fill_kernel(uint16_t* __restrict__ dst, int rows, int cols, long long ld, int dtype, int seed) {
+  const long long total = (long long)rows * cols;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
+    dst[(long long)r * ld + c] = selftest_encode(((r * 131 + c * 71 + seed) % 5) - 2, dtype);
+  }
+}
+
+// ref[m * N + n] = sum_k A[m,k] * B[k,n] + bias[n] in fp32 (exact for the small integers above).
+__global__ void selftest_ref_kernel(const uint16_t* __restrict__ a, long long lda, int a_trans, const uint16_t* __restrict__ b,
+                                    long long ldb, int b_trans, const uint16_t* __restrict__ bias, int M, int N, int K,
+                                    int dtype, float* __restrict__ ref) {
+  const long long total = (long long)M * N;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int m = (int)(i / N), n = (int)(i - (long long)m * N);
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const float x = load_in_as_float(a, a_trans ? (long long)k * lda + m : (long long)m * lda + k, dtype);
+      const float y = load_in_as_float(b, b_trans ? (long long)n * ldb + k : (long long)k * ldb + n, dtype);
+      acc += x * y;
+    }
+    if (bias != nullptr) acc += load_in_as_float(bias, n, dtype);
+    ref[i] = acc;
+  }
+}
+
+// Counts elements of out (fp32, bf16 or fp16; row-major contiguous) that differ from the reference rounded the same way.
+__global__ void selftest_compare_kernel(const void* __restrict__ out, int out_dtype, const float* __restrict__ ref,
+                                        long long total, int* __restrict__ mismatches) {
+  int bad = 0;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    if (out_dtype == 1) {
+      bad += reinterpret_cast<const float*>(out)[i] != ref[i];
+    } else {
+      bad += reinterpret_cast<const uint16_t*>(out)[i] != selftest_encode_float(ref[i], out_dtype);
+    }
+  }
+  if (bad) atomicAdd(mismatches, bad);
+}
+
 }  // namespace b200

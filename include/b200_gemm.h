@@ -30,6 +30,7 @@ extern "C" {
 #define B200_GEMM_ERR_LAUNCH (-5)         /* CUDA launch error (cudaGetLastError text via strerror) */
 #define B200_GEMM_ERR_DRIVER (-6)         /* driver entry point not found                           */
 #define B200_GEMM_ERR_TOO_LARGE (-7)      /* size beyond a stated fixed limit                       */
+#define B200_GEMM_ERR_SELFTEST (-8)   /* b200_gemm_selftest: a known-answer case gave a wrong result              */
 
 /* size of the ticket region at the start of a workspace */
 #define B200_GEMM_COUNTER_BYTES (1u << 20)
@@ -193,6 +194,18 @@ typedef struct b200_peer_handle {
 int b200_peer_export(const void* ptr, b200_peer_handle* handle);
 int b200_peer_open(const b200_peer_handle* handle, void** ptr);
 int b200_peer_close(void* ptr, const b200_peer_handle* handle);
+
+/* Known-answer self-test for hosts without a test harness of their own (a plug-in loaded into another engine calls it
+ * once at start-up). Runs 200 x 264 x 328 GEMMs on small-integer operands, for which fp32 accumulation is exact, through
+ * every tile family (16...256 wide, CTA pairs, both stage depths, ticket and cluster split-K, stream-K, swapped operands),
+ * the four layouts and both 16-bit dtypes, and compares each result bit for bit with a plain CUDA-core reference. This
+ * checks exactly what a wrong tensor-map, shared-memory-descriptor or instruction-descriptor encoding would break.
+ * Operands, outputs and workspace live in the library's built-in scratch array (nothing is allocated); the call
+ * launches on `cuda_stream` and synchronises it. Returns B200_GEMM_OK, B200_GEMM_ERR_SELFTEST, or the error of a failing
+ * launch; *failed_case (optional) receives the 1-based index of the failing case. Serialise with other users of the
+ * built-in scratch. The reference has no counterpart: its descriptors are generated by FlyDSL
+ * (kernels/gemm_a16w16_gfx950.py:378-705 are traced, not hand-encoded). */
+int b200_gemm_selftest(void* cuda_stream, int32_t* failed_case);
 
 /* Text for an error code; for B200_GEMM_ERR_LAUNCH the last CUDA error string seen by this thread. */
 const char* b200_gemm_strerror(int code);

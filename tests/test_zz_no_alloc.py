@@ -81,3 +81,23 @@ def test_static_scratch_needs_no_scratch_for_plain_tiles():
     assert rc == 0
     torch.cuda.synchronize()
     O.assert_close(out, O.reference_matmul(a_l, b_l, None, torch.bfloat16), case.k, "plain")
+
+
+@pytest.mark.gpu
+def test_library_selftest_passes_and_allocates_nothing():
+    """b200_gemm_selftest: known-answer GEMMs through every tile family inside the built-in scratch array."""
+    import ctypes as C
+
+    from flydsl_examples_b200 import _lib
+
+    lib = _lib.load()
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream()
+    failed = C.c_int32(0)
+    assert lib.b200_gemm_selftest(C.c_void_p(stream.cuda_stream), C.byref(failed)) == 0, f"case {failed.value}"
+    assert failed.value == -1
+    before = torch.cuda.memory_allocated()
+    free_before, _ = torch.cuda.mem_get_info()
+    assert lib.b200_gemm_selftest(C.c_void_p(stream.cuda_stream), None) == 0
+    free_after, _ = torch.cuda.mem_get_info()
+    assert torch.cuda.memory_allocated() == before and free_after == free_before  # no device memory was taken
