@@ -86,7 +86,7 @@ constexpr KernelFn kfn() {
 static const Variant kVariants[] = {
     // The first entry of a (tile, cta_group) is the default when the policy leaves tile_k at 0.
     B200_VARIANT_K128(16, 5),     B200_VARIANT_K128(32, 5),    B200_VARIANT_K128(64, 4),    B200_VARIANT_K128(128, 3),
-    B200_VARIANT_K64(256, 1, 4),  B200_VARIANT_K64(128, 2, 8), B200_VARIANT_K64(256, 2, 6),
+    B200_VARIANT_K64(256, 1, 4),  B200_VARIANT_K64(128, 2, 8), B200_VARIANT_K64(256, 2, 6),  B200_VARIANT_K64(192, 2, 6),
     B200_VARIANT_K64(16, 1, 8),   B200_VARIANT_K64(32, 1, 8),  B200_VARIANT_K64(64, 1, 8),  B200_VARIANT_K64(128, 1, 6),
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
@@ -187,7 +187,8 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
     r->P = (int)a->n, r->Q = (int)a->m;
     r->u_mn = b_mn, r->v_mn = a_mn;
   }
-  if (r->v_mn && pl.tile_n / pl.cta_group < 64) return B200_GEMM_ERR_BAD_POLICY;  // an MN-major box is 64 elements wide
+  // an MN-major operand is fetched in boxes 64 elements wide: each CTA's share of tile_n must be whole boxes
+  if (r->v_mn && (pl.tile_n / pl.cta_group) % 64 != 0) return B200_GEMM_ERR_BAD_POLICY;
 
   pl.tiles_p = (r->P + pl.tile_m - 1) / pl.tile_m;
   pl.tiles_q = (r->Q + pl.tile_n - 1) / pl.tile_n;
@@ -204,7 +205,8 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
   if (stages < 2) return B200_GEMM_ERR_BAD_POLICY;
   pl.stages = stages;
   pl.smem_bytes = dyn_smem_bytes(pl.tile_n, stages, pl.cta_group, pl.tile_k);
-  pl.tmem_cols = 2 * pl.tile_n < 32 ? 32 : 2 * pl.tile_n;
+  pl.tmem_cols = 32;
+  while (pl.tmem_cols < 2 * pl.tile_n) pl.tmem_cols *= 2;  // allocated in powers of two
 
   int sms = sm_count_hint;
   if (need_sm_count && sms <= 0) return B200_GEMM_ERR_LAUNCH;
@@ -575,6 +577,7 @@ int b200_gemm_selftest(void* cuda_stream, int32_t* failed_case) {
       {128, 2, 1, 0, 0, 0, 0, 0, 1, 0}, {256, 2, 1, 0, 0, 0, 0, 1, 1, 0},  {128, 1, 1, 0, 0, 0, 64, 0, 0, 0},
       {64, 1, 3, 0, 0, 0, 0, 1, 1, 0},  {64, 1, 2, 2, 0, 0, 0, 0, 1, 0},   {128, 1, 1, 0, 1, 0, 0, 0, 1, 0},
       {16, 1, 1, 0, 0, 0, 0, 0, 1, 1},  {32, 1, 2, 2, 0, 0, 64, 1, 0, 1},  {16, 1, 4, 2, 0, 1, 0, 1, 1, 1},
+      {192, 2, 1, 0, 0, 0, 0, 0, 1, 1},
   };
   if (failed_case) *failed_case = -1;
   void* scratch_v = nullptr;

@@ -282,7 +282,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
   using L = SmemLayout<TILE_Q, STAGES, CG, TK>;
   constexpr int CW = TILE_Q >= 32 ? 32 : 16;  // columns per tcgen05.ld
   constexpr int NCHUNK = TILE_Q / CW;
-  constexpr uint32_t kTmemCols = (2 * TILE_Q) < 32 ? 32 : 2 * TILE_Q;  // power of two for every TILE_Q in the menu
+  // TMEM is allocated in powers of two of at least 32 columns: two accumulators of TILE_Q columns each
+  constexpr uint32_t kTmemCols = 2 * TILE_Q <= 32 ? 32 : 2 * TILE_Q <= 64 ? 64 : 2 * TILE_Q <= 128 ? 128 : 2 * TILE_Q <= 256 ? 256 : 512;
   constexpr uint32_t kTxBytes = CG * L::kStageBytes;  // a pair's two CTAs both report to the leader's barrier
   constexpr int kVRows = L::kVRows;
   constexpr int kSlotVec = NCHUNK * (CW / 4) * kTileP;  // float4 per partial slot of one CTA

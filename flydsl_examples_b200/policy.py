@@ -19,7 +19,7 @@ TILE_K = 64   # one TMA box: a 128-byte swizzle span of 16-bit data
 TILE_N_MENU = (16, 32, 64, 128, 256)
 MAX_STAGES = {16: 5, 32: 5, 64: 4, 128: 3, 256: 4}            # one CTA per tile, default stage depth
 MAX_STAGES_K64 = {16: 8, 32: 8, 64: 8, 128: 6, 256: 4}        # one CTA per tile, 64-deep stages
-MAX_STAGES_PAIR = {128: 8, 256: 6}                            # a CTA pair per 256-row tile (cta_group 2)
+MAX_STAGES_PAIR = {128: 8, 192: 6, 256: 6}                    # a CTA pair per 256-row tile (cta_group 2)
 
 
 def tile_k(tile_n: int, cta_group: int = 1, requested: int = 0) -> int:
@@ -150,8 +150,8 @@ def stream_k_walk(cta: int, grid: int, tiles: int, kb_total: int, sk_tiles: int)
 
 def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
     """Return None when the policy is runnable for this problem, else the reason."""
-    if pol.tile_n not in TILE_N_MENU:
-        return f"tile_n must be one of {TILE_N_MENU}, got {pol.tile_n}"
+    if pol.tile_n not in TILE_N_MENU and not (pol.cta_group == 2 and pol.tile_n in MAX_STAGES_PAIR):
+        return f"tile_n must be one of {TILE_N_MENU} (or {tuple(MAX_STAGES_PAIR)} with cta_group 2), got {pol.tile_n}"
     if pol.cta_group not in (1, 2):
         return f"cta_group must be 1 or 2, got {pol.cta_group}"
     stage_menu = MAX_STAGES if pol.cta_group == 1 else MAX_STAGES_PAIR
@@ -179,8 +179,8 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
     a_mn = layout[0] == "t"
     b_mn = layout[1] == "n"
     v_mn = a_mn if pol.swap_ab else b_mn
-    if v_mn and pol.tile_n // pol.cta_group < 64:
-        return "fewer than 64 tile_n columns per CTA needs the tile_n-side operand to be K-contiguous"
+    if v_mn and (pol.tile_n // pol.cta_group) % 64 != 0:
+        return "a tile_n-side operand that is not K-contiguous needs a multiple of 64 tile_n columns per CTA"
     if 2 * pol.tile_n > TMEM_COLUMNS:
         return "two accumulators do not fit in 512 TMEM columns"
     return None
@@ -190,7 +190,8 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
 # measured: the tensor pipe needs 128 cycles per 128 x 256 x 16 MMA, and one SM takes in about 64 bytes per clock
 # from L2, i.e. 2 * (128 + tile_n) cycles for the 128 + tile_n operand rows of a block (a CTA of a pair loads half of
 # the tile_n rows). Every single-CTA tile is bound by the second; the 256 x 256 pair balances the two.
-_KBLOCK_CYCLES = {(1, 256): 800.0, (2, 256): 590.0, (1, 128): 540.0, (1, 64): 400.0, (1, 32): 340.0, (1, 16): 310.0}
+_KBLOCK_CYCLES = {(1, 256): 800.0, (2, 256): 590.0, (2, 192): 530.0, (1, 128): 540.0, (1, 64): 400.0, (1, 32): 340.0,
+                  (1, 16): 310.0}
 _FIXED_CYCLES = 6000.0  # launch tail, pipeline fill, last epilogue
 
 
@@ -218,7 +219,8 @@ def _estimate_cycles(p_ext: int, q: int, kb: int, cta_group: int, tile_n: int, n
     # (partial write, fences and ticket, read-back) about 5 us
     # (the last arriver reads split slabs of 128 x tile_n floats at about 24 bytes per clock)
     fixup = 0.0 if split <= 1 else (1500.0 + 200.0 * split) if (cta_group == 1 and tile_n <= 64) else (8000.0 + 21.0 * split * tile_n)
-    return _FIXED_CYCLES + waves * (-(-kb // split) * _KBLOCK_CYCLES[(cta_group, tile_n)] + epilogue) + fixup
+    pair_start = 2500.0 if cta_group == 2 else 0.0  # a cluster launch reaches its first MMA about 1.5 us later
+    return _FIXED_CYCLES + pair_start + waves * (-(-kb // split) * _KBLOCK_CYCLES[(cta_group, tile_n)] + epilogue) + fixup
 
 
 def heuristic(m: int, n: int, k: int, layout: str = "nt", num_sms: int = NUM_SMS_DEFAULT) -> Policy:
@@ -239,6 +241,8 @@ def heuristic(m: int, n: int, k: int, layout: str = "nt", num_sms: int = NUM_SMS
         cands = [(1, t) for t in menu if t <= max(64, 1 << (max(q, 1) - 1).bit_length())]
         if p_ext > TILE_M and q > 128:
             cands.append((2, 256))
+            if not v_mn:
+                cands.append((2, 192))  # 96 columns per CTA: K-contiguous tile_n-side operand only
         best = min(cands, key=lambda c: (_estimate_cycles(p_ext, q, kb, c[0], c[1], num_sms), -c[1], -c[0]))
         cta_group, tile_n = best
     walkers = num_sms // cta_group

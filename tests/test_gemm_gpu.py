@@ -289,6 +289,28 @@ def test_cta_pair_shapes(dtype, idx):
                      repeats=2, prefill="randn")
 
 
+PAIR_192 = [  # 256 x 192 pair tiles: 96 columns per CTA, so B must be K-contiguous ('nt', 'tt')
+    (512, 768, 520, {"tile_n": 192, "cta_group": 2}),
+    (700, 500, 1000, {"tile_n": 192, "cta_group": 2}),                      # ragged in M and N
+    (1000, 3000, 4100, {"tile_n": 192, "cta_group": 2}),                    # config 4's shape: 64 pair tiles
+    (1000, 3000, 4100, {"tile_n": 192, "cta_group": 2, "stream_k": True}),
+    (512, 384, 4096, {"tile_n": 192, "cta_group": 2, "split_k": 3}),
+    (2048, 1920, 512, {"tile_n": 192, "cta_group": 2, "group_m": 4, "stages": 3}),
+]
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("idx", range(len(PAIR_192)))
+def test_cta_pair_192_wide_tiles(dtype, idx):
+    m, n, k, kw = PAIR_192[idx]
+    for layout in ("nt", "tt"):
+        for out_dtype in (None, "fp32"):
+            run_case(O.Case("pair192", dtype, layout, m, n, k, seed=450 + idx, bias_std=0.5, out_dtype=out_dtype, user_kwargs=kw),
+                     repeats=2, prefill="randn")
+    with pytest.raises(AssertionError):  # N-contiguous B cannot be cut into 96-column shares
+        run_case(O.Case("pair192", dtype, "nn", m, n, k, seed=1, user_kwargs=kw))
+
+
 def test_default_policy_picks_a_pair_for_large_shapes():
     a = torch.empty(8192, 4096, dtype=torch.bfloat16, device=DEV)
     b = torch.empty(4096, 4096, dtype=torch.bfloat16, device=DEV).t()
