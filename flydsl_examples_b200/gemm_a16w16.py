@@ -154,7 +154,9 @@ def resolve_policy(m: int, n: int, k: int, dtype: torch.dtype, layout: str, user
         rec = _policy.tuned_lookup(_dtype_name(dtype), layout, m, n, k)
         if rec is not None:
             control = {key: val for key, val in user_kwargs.items() if key in _policy.CONTROL_KEYS}
-            return _policy.from_user_kwargs({**rec, **control}, m, n, k, layout, num_sms)
+            pol = _policy.from_user_kwargs({**rec, **control}, m, n, k, layout, num_sms)
+            if _policy.validate(pol, m, n, k, layout) is None:  # a row tuned for another layout may not fit this one
+                return pol
     return _policy.from_user_kwargs(user_kwargs, m, n, k, layout, num_sms)
 
 

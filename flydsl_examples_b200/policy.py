@@ -321,7 +321,13 @@ def tuned_lookup(dtype: str, layout: str, m: int, n: int, k: int) -> Optional[di
     speed, so a row tuned for one serves the other."""
     if not _TUNED_LOADED:
         load_tuned()
-    rec = _TUNED.get((dtype, layout, m, n, k))
-    if rec is None:
-        rec = _TUNED.get(("fp16" if dtype == "bf16" else "bf16", layout, m, n, k))
-    return rec
+    other = "fp16" if dtype == "bf16" else "bf16"
+    # Rows tuned for another layout of the same problem are the next best thing (the main loop differs only in the
+    # shared-memory image of an operand); the caller checks that the policy is valid for its own layout.
+    layouts = [layout] + [l for l in (layout[0] + "t", "nt", "tt", "nn", "tn") if l != layout]
+    for lay in dict.fromkeys(layouts):
+        for dt in (dtype, other):
+            rec = _TUNED.get((dt, lay, m, n, k))
+            if rec is not None:
+                return rec
+    return None

@@ -202,6 +202,25 @@ def test_tuned_table_roundtrip(tmp_path):
     assert pol.swap_ab and pol.split_k == 16 and pol.stages == 8
 
 
+def test_tuned_rows_serve_other_layouts_only_when_valid():
+    import torch
+
+    from flydsl_examples_b200.gemm_a16w16 import resolve_policy
+
+    # the shipped table has config 3 tuned for 'nt' only (tile 16, swapped, 16-CTA cluster)
+    nt = resolve_policy(32, 384, 7168, torch.bfloat16, "nt", {})
+    assert (nt.tile_n, nt.swap_ab, nt.split_mode) == (16, True, "cluster")
+    # 'nn' keeps A K-contiguous, which is all a swapped narrow tile needs: the row is reused
+    nn = resolve_policy(32, 384, 7168, torch.float16, "nn", {})
+    assert (nn.tile_n, nn.swap_ab, nn.split_k) == (nt.tile_n, True, nt.split_k)
+    # with an M-contiguous A the narrow tile is not runnable: the heuristic answers instead, with a valid policy
+    tn = resolve_policy(32, 384, 7168, torch.bfloat16, "tn", {})
+    assert tn.tile_n >= 64 and P.validate(tn, 32, 384, 7168, "tn") is None
+    # config 4: the 256x192 pair of the 'nt' row needs a K-contiguous B; 'nn' has its own row
+    assert resolve_policy(1000, 3000, 4100, torch.float16, "tt", {}).tile_n == 192
+    assert resolve_policy(1000, 3000, 4100, torch.float16, "nn", {}).tile_n == 256
+
+
 @pytest.mark.parametrize(("tiles", "kb", "cap"), [(256, 64, 148), (96, 65, 148), (3, 112, 148), (1792, 128, 148), (149, 2, 148),
                                                   (148, 64, 148), (1, 1000, 148), (300, 5, 148), (7, 3, 148), (14336, 128, 148)])
 def test_stream_k_walk_covers_every_k_block_once(tiles, kb, cap):
