@@ -267,7 +267,7 @@ class Workload:
             self.per_rank_flops = float(case.flops)
             self.plan = plan(a, b, case.layout, case.user_kwargs, out_dtype=case.torch_out_dtype, bias=bias)
             self.gemm_launches_per_step = 1
-            self.launches_per_step = 1 + self.plan["a_repacked"] + self.plan["b_repacked"]
+            self.launches_per_step = 1 + (1 if self.plan["a_repacked"] or self.plan["b_repacked"] else 0)  # one repack launch covers both operands
             self.partition = "one GEMM per GPU" + (" (independent replicas)" if world > 1 else "")
             self.algorithmic_bytes = case.algorithmic_bytes
             ins = [a, b]

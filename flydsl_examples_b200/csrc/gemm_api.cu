@@ -329,7 +329,7 @@ static int set_cuda_error(cudaError_t e) {
   return B200_GEMM_ERR_LAUNCH;
 }
 
-// A fully resolved call: everything the launch needs, so that repeating it costs one (or up to three) kernel launches
+// A fully resolved call: everything the launch needs, so that repeating it costs one kernel launch (two when an operand must be repacked first)
 // and no host-side planning or tensor-map encoding.
 struct RepackJob {
   const uint16_t* src;
@@ -473,9 +473,11 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
 }
 
 static int run(const b200_gemm_handle* h, cudaStream_t stream) {
-  for (int i = 0; i < h->n_repack; ++i) {
-    const RepackJob& j = h->repack[i];
-    repack_rows_kernel<<<j.blocks, 256, 0, stream>>>(j.src, j.src_ld, j.dst, j.dst_ld, j.rows, j.cols);
+  if (h->n_repack > 0) {  // one launch for both operands when both need it
+    const RepackJob& j0 = h->repack[0];
+    const RepackJob j1 = h->n_repack > 1 ? h->repack[1] : RepackJob{nullptr, nullptr, 0, 0, 0, 0, 0};
+    repack_rows_kernel<<<j0.blocks + j1.blocks, 256, 0, stream>>>(j0.src, j0.src_ld, j0.dst, j0.dst_ld, j0.rows, j0.cols, j0.blocks,
+                                                                  j1.src, j1.src_ld, j1.dst, j1.dst_ld, j1.rows, j1.cols);
     cudaError_t re = cudaGetLastError();
     if (re != cudaSuccess) return set_cuda_error(re);
   }

@@ -947,11 +947,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
 // Aligned repack: copies a 16-bit matrix whose base or pitch is not 16-byte aligned (TMA cannot describe it)
 // into a scratch image with a pitch that is a multiple of 8 elements. rows x cols, cols contiguous.
 // The reference rejects such operands (kernels/gemm_a16w16_gfx950.py:1322-1372); this path accepts them.
-__global__ void repack_rows_kernel(const uint16_t* __restrict__ src, long long src_ld, uint16_t* __restrict__ dst,
-                                   long long dst_ld, int rows, int cols) {
+__device__ __forceinline__ void repack_rows_body(const uint16_t* __restrict__ src, long long src_ld, uint16_t* __restrict__ dst,
+                                                 long long dst_ld, int rows, int cols, int block, int nblocks) {
   const int chunks = (cols + 7) >> 3;
   const long long total = (long long)rows * chunks;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+  for (long long i = block * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)nblocks * blockDim.x) {
     const int r = (int)(i / chunks);
     const int c0 = (int)(i - (long long)r * chunks) << 3;
     const uint16_t* s = src + (long long)r * src_ld + c0;
@@ -969,6 +969,16 @@ __global__ void repack_rows_kernel(const uint16_t* __restrict__ src, long long s
     }
     *reinterpret_cast<uint4*>(dst + (long long)r * dst_ld + c0) = make_uint4(w[0], w[1], w[2], w[3]);
   }
+}
+
+// One launch repacks up to two operands: blocks [0, blocks0) take the first job, the rest the second.
+__global__ void repack_rows_kernel(const uint16_t* __restrict__ src0, long long src_ld0, uint16_t* __restrict__ dst0,
+                                   long long dst_ld0, int rows0, int cols0, int blocks0, const uint16_t* __restrict__ src1,
+                                   long long src_ld1, uint16_t* __restrict__ dst1, long long dst_ld1, int rows1, int cols1) {
+  if ((int)blockIdx.x < blocks0)
+    repack_rows_body(src0, src_ld0, dst0, dst_ld0, rows0, cols0, (int)blockIdx.x, blocks0);
+  else
+    repack_rows_body(src1, src_ld1, dst1, dst_ld1, rows1, cols1, (int)blockIdx.x - blocks0, (int)gridDim.x - blocks0);
 }
 
 // ---------------------------------------------------------------------------------------------------------
