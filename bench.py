@@ -5,21 +5,29 @@
                     [--impl ours|reference]
 
 Prints ONE JSON line. A step is one pass of the hot path (one GEMM call) over one batch of synthetic input.
-  N = 1  default workload c2: bf16 'nt' 2048x4096x4096 + bias, bf16 out (the compute-bound benchmark config).
-  N > 1  default workload c5_nshard: bf16 'nt' 16384x28672x8192, B sharded along N over the ranks, no collective;
-         `value` is total FLOPs of the whole GEMM / max-over-ranks time (fixed total work: strong scaling).
+  N = 1  default workload c5: bf16 'nt' 16384x28672x8192, the whole GEMM on one GPU (the largest configuration of the
+         benchmark list that fits one GPU, and the very GEMM the N > 1 runs shard). The same line carries a `configs`
+         dict with device-timed records of the small configurations (c1, c2, c3, c4 in its four layouts), each with its
+         own roofline entry, and a `sustained` record (the same step looped for more than a second).
+  N > 1  default workload c5_nshard: the same GEMM with B sharded along N over the ranks, no collective; `value` is
+         total FLOPs of the whole GEMM / max-over-ranks time (fixed total work: strong scaling). The line also carries
+         `kshard` and `kshard_fused` records: the K-sharded modes (NCCL reduce-scatter of fp32 partials; partial sums
+         stored into the owner's memory over NVLink by the GEMM epilogue), each with a sampled-row parity check
+         against the CPU oracle.
 `value`   device-timed (CUDA events on the launching stream) with inputs resident in HBM; inputs rotate over a set
           of buffers larger than L2 for the small configs, and are larger than L2 by themselves for c5.
 `e2e`     same metric through the public Python call with HOST (pinned) inputs: host->device copies of A, B, bias
           and the device->host read of C are inside the timed region.
 `--impl reference`: the reference has no CPU implementation of its kernel; its tests check against torch.mm on
 the same tensors (test_gemm_a16w16_gfx950.py:82-94). That CPU computation (oracle.reference_matmul: fp32
-torch.matmul + bias) is what the reference arm times, on all host threads torch uses, on a bounded sample.
+torch.matmul + bias) is what the reference arm times, on all host threads this process may use, on a bounded sample.
 """
 from __future__ import annotations
 
 import argparse
+import gc
 import json
+import math
 import os
 import statistics
 import sys
@@ -34,9 +42,13 @@ if str(ROOT) not in sys.path:
 import torch  # noqa: E402
 
 L2_BYTES_NOMINAL = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
-# under profiles/ (None until captured for that workload).
-NCU_TRAFFIC_BYTES = {"c2": 53.5e6}  # profiles/gemm_sm100_kernel_config2.md
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel, from ncu captures of these workloads
+# (None where no capture exists). The c4 figures are the GEMM launch alone; its repack launch moves 33.9 MB more.
+NCU_TRAFFIC_BYTES = {"c2": 53.5e6, "c3": 6.04e6, "c4_nt": 32.9e6, "c5": 17.1e9}
+SMALL_CONFIGS = ("c1", "c2", "c3", "c4_nn", "c4_nt", "c4_tn", "c4_tt")
+SHARDED = ("c5_nshard", "c5_kshard", "c5_kshard_fused")
+PLAN_KEYS = ("tile_m", "tile_n", "tile_k", "stages", "split_k", "cluster_split", "swap_ab", "group_m", "grid", "num_units",
+             "stream_k", "sk_tiles", "a_repacked", "b_repacked")
 
 
 def measured_peaks() -> dict:
@@ -46,6 +58,15 @@ def measured_peaks() -> dict:
         return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained"),
                 "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def host_threads() -> int:
+    """Threads this process may run on (its CPU affinity), not what OMP_NUM_THREADS says: torch.distributed.run sets
+    that variable to 1 for every rank."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 class ClockSampler:
@@ -121,9 +142,11 @@ def physical_gpu_index(local: int) -> int:
 
 def cpu_reference_run(case, seconds_budget: float = 12.0, max_reps: int = 20) -> dict:
     """Time the CPU computation the reference's tests use as ground truth (fp32 torch.matmul + bias) on a bounded
-    sample of `case`: all of it when one pass is short, else a slab of rows scaled to fit the budget."""
+    sample of `case`: all of it when one pass is short, else a slab of rows scaled to fit the budget. Uses every host
+    thread this process may run on."""
     from oracle import oracle as O
 
+    torch.set_num_threads(host_threads())
     m = case.m
     flops_full = case.flops
     # probe speed on a small slab to size the sample
@@ -176,6 +199,11 @@ def clone_with_layout(t: torch.Tensor) -> torch.Tensor:
     return torch.as_strided(flat, t.shape, t.stride(), t.storage_offset())
 
 
+def workload_label(workload: str, case) -> str:
+    return (f"{workload}: {case.dtype} '{case.layout}' M={case.m} N={case.n} K={case.k}"
+            f"{' +bias' if case.bias_std is not None else ''} -> {case.out_dtype or case.dtype}")
+
+
 class Workload:
     """One benchmark workload on one rank: resident-input step, host-input step, and the numbers that describe it."""
 
@@ -186,7 +214,7 @@ class Workload:
 
         self.name, self.world, self.rank, self.device = name, world, rank, device
         self.extra = {}
-        big = name in ("c5", "c5_nshard", "c5_kshard", "c5_kshard_fused")
+        big = name in ("c5",) + SHARDED
         self.case = case = O.CONFIGS["c5" if big else name]
         if args.policy:
             import dataclasses
@@ -194,13 +222,17 @@ class Workload:
         out_es = 4 if case.torch_out_dtype is torch.float32 else 2
         if big:
             # Synthetic N(0, 0.02) operands drawn on the device; C5's operands and output exceed L2 by themselves.
+            # A is the same on every rank (same seed); a rank's slab of B comes from a seed of its own.
             torch.manual_seed(case.seed)
             a_full = (torch.randn(case.m, case.k, device=device, dtype=torch.float32) * case.a_std).to(torch.bfloat16)
+            self.a_full = a_full
             self.rotation = "inputs larger than L2"
             self.total_flops = float(case.flops)
+            torch.manual_seed(case.seed + 1000 * (rank + 1))
             if name in ("c5_kshard", "c5_kshard_fused") and world > 1:
                 k0, k1 = MG.shard_bounds(case.k, world, rank, 64)
                 b_store = (torch.randn(case.n, k1 - k0, device=device, dtype=torch.float32) * case.b_std).to(torch.bfloat16)
+                self.b_store, self.k_range = b_store, (k0, k1)
                 a_loc, b_loc, chunks = a_full[:, k0:k1], b_store.t(), args.chunks
                 self.result = None
                 self.per_rank_flops = 2.0 * case.m * case.n * (k1 - k0)
@@ -416,6 +448,185 @@ def timed(stream, device, fn, steps, world, finish=None):
     return ms / steps
 
 
+def roofline_entry(workload: str, case, flops_per_launch: float, sec_per_launch: float, peaks: dict, long_run: bool) -> dict:
+    """Roofline of one GEMM launch: HBM-bound for the small-M decode shape (c3), tensor-bound otherwise. Runs longer
+    than a second are held against the sustained cuBLAS figure, shorter ones against the burst figure."""
+    traffic = NCU_TRAFFIC_BYTES.get("c5" if workload in SHARDED else workload)
+    if workload == "c3":
+        achieved = case.algorithmic_bytes / sec_per_launch / 1e9
+        return {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": traffic, "peak_source": f"{peaks['source']} copy bandwidth"}
+    achieved = flops_per_launch / sec_per_launch / 1e12
+    sustained = peaks.get("bf16_tflops_sustained")
+    peak = sustained if (long_run and sustained) else peaks["bf16_tflops"]
+    return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            "traffic": traffic if workload not in SHARDED else None,
+            "peak_source": f"{peaks['source']} cuBLAS bf16 ({'sustained' if long_run and sustained else 'burst'})"}
+
+
+def sustained_record(w: Workload, ms_per_step: float, stream, device, world, local, peaks, use_graph: bool,
+                     seconds: float = 1.2) -> dict:
+    """The same step, looped back to back for more than `seconds`, with the SM clock sampled meanwhile."""
+    n = max(3, int(math.ceil(seconds * 1e3 / max(ms_per_step, 1e-4))))
+    replay, per = None, 1
+    if use_graph:
+        per = 500
+        replay = graphed(w.step, per, device)
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        if replay is not None:
+            reps = max(1, n // per)
+            ms = timed(stream, device, replay, reps, world) / per
+            n = reps * per
+        else:
+            ms = timed(stream, device, w.step, n, world)
+    tf = w.total_flops / (ms * 1e-3) / 1e12
+    rec = {"steps": n, "seconds": ms * n * 1e-3, "ms_per_step": ms, "value": tf, "unit": "TFLOP/s", "clocks": clocks.summary()}
+    per_gpu = w.per_rank_flops / (ms * 1e-3) / 1e12
+    if peaks.get("bf16_tflops_sustained"):
+        rec["per_gpu_frac_of_sustained_peak"] = per_gpu / peaks["bf16_tflops_sustained"]
+    rec["per_gpu_frac_of_burst_peak"] = per_gpu / peaks["bf16_tflops"]
+    return rec
+
+
+def small_config_record(name: str, args, device, stream, local, peaks) -> dict:
+    """Device-timed record of one small configuration on this GPU: a short burst (20 calls) and a region of at least
+    a quarter of a second with the SM clock sampled, each call on the next of the rotating input sets."""
+    from flydsl_examples_b200.gemm_a16w16 import check_status
+
+    saved_policy, args.policy = args.policy, None
+    try:
+        w = Workload(name, args, 1, 0, device)
+    finally:
+        args.policy = saved_policy
+    case = w.case
+    w.step()
+    check_status(device)
+    for _ in range(20):
+        w.step()
+    use_graph = name in ("c1", "c3")  # one call is shorter than its host-side launch
+    if use_graph:
+        per = 500
+        replay = graphed(w.step, per, device)
+        burst_ms = timed(stream, device, replay, 1, 1) / per
+        reps = max(1, int(math.ceil(250.0 / (burst_ms * per))))
+        with ClockSampler(physical_gpu_index(local)) as clocks:
+            long_ms = timed(stream, device, replay, reps, 1) / per
+        calls = reps * per
+    else:
+        burst_ms = timed(stream, device, w.step, 20, 1)
+        calls = max(200, int(math.ceil(250.0 / burst_ms)))
+        with ClockSampler(physical_gpu_index(local)) as clocks:
+            long_ms = timed(stream, device, w.step, calls, 1)
+    check_status(device)
+    best = min(burst_ms, long_ms)
+    roof = roofline_entry(name, case, float(case.flops), best * 1e-3, peaks, False)
+    rec = {
+        "workload": workload_label(name, case),
+        "us_per_call": best * 1e3,
+        "us_per_call_burst": burst_ms * 1e3,
+        "us_per_call_long": long_ms * 1e3,
+        "long_region": {"calls": calls, "seconds": long_ms * calls * 1e-3, "clocks": clocks.summary()},
+        "tflops": case.flops / (best * 1e-3) / 1e12,
+        "gbs": case.algorithmic_bytes / (best * 1e-3) / 1e9,
+        "roofline": roof,
+        "launch": "CUDA graph of 500 calls" if use_graph else "one host call per GEMM",
+        "kernels_per_call": w.launches_per_step,
+        "l2": w.rotation,
+        "plan": {k: w.plan[k] for k in PLAN_KEYS},
+    }
+    if roof["bound"] == "tensor" and peaks.get("bf16_tflops_sustained"):
+        rec["long_frac_of_sustained_peak"] = case.flops / (long_ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"]
+    del w
+    gc.collect()
+    torch.cuda.empty_cache()
+    return rec
+
+
+def kshard_parity(w: Workload, device, world: int, rank: int, n_rows: int = 64) -> dict | None:
+    """Sampled full rows of a K-sharded result against the CPU oracle (fp32 matmul of the up-cast operands, one
+    cast), at the benchmark tolerance. Every rank contributes the same number of its own rows; rank 0 gathers them
+    together with every rank's K slab of B and checks. Returns the verdict on rank 0, None elsewhere."""
+    import torch.distributed as dist
+
+    from oracle import oracle as O
+
+    res, case = w.result, w.case
+    per_rank = max(1, n_rows // world)
+    g = torch.Generator().manual_seed(1234 + rank)
+    local_rows = torch.randint(0, res.out.shape[0], (per_rank,), generator=g)
+    block = res.out.shape[0] // len(res.row_ranges)
+    global_rows = torch.tensor([res.row_ranges[int(i) // block][0] + int(i) % block for i in local_rows], dtype=torch.int64)
+    got = res.out[local_rows.to(device)].contiguous()
+    got_all = torch.empty((world,) + tuple(got.shape), dtype=got.dtype, device=device)
+    dist.all_gather_into_tensor(got_all, got)
+    rows_all = torch.empty((world, per_rank), dtype=torch.int64, device=device)
+    dist.all_gather_into_tensor(rows_all, global_rows.to(device))
+    verdict = None
+    if rank == 0:
+        b_full = torch.empty((case.n, case.k), dtype=torch.bfloat16)  # B as stored: [N, K]
+    for r in range(world):  # one slab at a time: K/world columns of the stored B from rank r
+        slab = w.b_store if r == rank else torch.empty_like(w.b_store)
+        dist.broadcast(slab, src=r)
+        if rank == 0:
+            k0 = r * w.b_store.shape[1]
+            b_full[:, k0:k0 + slab.shape[1]] = slab.cpu()
+        del slab
+    if rank == 0:
+        torch.set_num_threads(host_threads())
+        rows = rows_all.reshape(-1).cpu()
+        ref = O.reference_matmul(w.a_full[rows.to(device)].cpu(), b_full.t(), None, torch.bfloat16)
+        cmp = O.compare(got_all.reshape(-1, case.n).cpu(), ref, case.k)
+        verdict = {"ok": bool(cmp["ok"]), "rows_checked": int(rows.numel()), "mismatches": cmp["mismatches"],
+                   "max_abs": cmp["max_abs"], "rtol": cmp["rtol"], "atol": cmp["atol"],
+                   "oracle": "CPU fp32 matmul of the up-cast operands, cast once to bf16"}
+    dist.barrier()
+    return verdict
+
+
+def kshard_record(mode: str, args, world, rank, local, device, stream, peaks) -> dict | None:
+    """One K-sharded mode of c5 on all ranks: at least five timed steps (max over ranks) and the parity check."""
+    import torch.distributed as dist
+
+    from flydsl_examples_b200.gemm_a16w16 import check_status
+
+    saved_policy, args.policy = args.policy, None
+    try:
+        w = Workload(mode, args, world, rank, device)
+    finally:
+        args.policy = saved_policy
+    w.plan_chunks = args.chunks
+    w.step()
+    check_status(device)
+    parity = kshard_parity(w, device, world, rank)
+    for _ in range(2):
+        w.step()
+    steps = max(5, min(args.steps, 10))
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        ms = timed(stream, device, w.step, steps, world)
+    check_status(device)
+    rec = {
+        "workload": workload_label(mode, w.case),
+        "partition": w.partition,
+        "steps": steps,
+        "ms_per_step": ms,
+        "value": w.total_flops / (ms * 1e-3) / 1e12,
+        "unit": "TFLOP/s",
+        "reduce_bytes_per_rank": w.extra["reduce_bytes_per_rank"],
+        "nvlink_gbs_per_rank": w.extra["reduce_bytes_per_rank"] / (ms * 1e-3) / 1e9,
+        "gemm_launches_per_step": w.gemm_launches_per_step,
+        "clocks": clocks.summary(),
+        "parity": parity,
+    }
+    if hasattr(w, "slots"):
+        dist.barrier()
+        w.slots.close()
+    del w
+    gc.collect()
+    torch.cuda.empty_cache()
+    dist.barrier()
+    return rec if rank == 0 else None
+
+
 def run_ours(args) -> dict:
     import torch.distributed as dist
 
@@ -429,11 +640,18 @@ def run_ours(args) -> dict:
     _lib.load()  # fail loudly if the CUDA library is missing
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    cpu = None
     if world > 1:
+        if rank == 0 and not args.no_cpu_baseline:
+            # A short sample, taken while the other ranks wait on the host in the rendezvous below (not at a GPU barrier).
+            from oracle import oracle as O
+
+            cpu = cpu_reference_run(O.CONFIGS["c5"], seconds_budget=4.0)
         dist.init_process_group("nccl", device_id=device)
     assert args.gpus == world, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}"
 
-    workload = args.workload or ("c2" if world == 1 else "c5_nshard")
+    default_run = args.workload is None and args.policy is None
+    workload = args.workload or ("c5" if world == 1 else "c5_nshard")
     peaks = measured_peaks()
     stream = torch.cuda.current_stream(device)
     w = Workload(workload, args, world, rank, device)
@@ -458,6 +676,10 @@ def run_ours(args) -> dict:
             ms_per_step = timed(stream, device, w.step, args.steps, world)
     check_status(device)
     value = w.total_flops / (ms_per_step * 1e-3) / 1e12
+    sustained = None
+    if not args.no_sustained:
+        sustained = sustained_record(w, ms_per_step, stream, device, world, local, peaks, replay is not None)
+        check_status(device)
 
     # ---------------------------------------------------------------- end to end: host buffers in, host result out
     w.prepare_e2e()
@@ -473,19 +695,8 @@ def run_ours(args) -> dict:
 
     # ---------------------------------------------------------------- roofline of the dominant kernel (the GEMM)
     sec_per_launch = ms_per_step * 1e-3 / w.gemm_launches_per_step
-    if workload == "c3":
-        achieved = case.algorithmic_bytes / sec_per_launch / 1e9
-        roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get(workload),
-                    "peak_source": f"{peaks['source']} copy bandwidth"}
-    else:
-        achieved = w.per_rank_flops / w.gemm_launches_per_step / sec_per_launch / 1e12
-        long_run = ms_per_step * 1e-3 * args.steps > 1.0
-        sustained = peaks.get("bf16_tflops_sustained")
-        peak = sustained if (long_run and sustained) else peaks["bf16_tflops"]
-        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "traffic": NCU_TRAFFIC_BYTES.get(workload),
-                    "peak_source": f"{peaks['source']} cuBLAS bf16 ({'sustained' if long_run and sustained else 'burst'})"}
+    long_run = ms_per_step * 1e-3 * args.steps > 1.0
+    roofline = roofline_entry(workload, case, w.per_rank_flops / w.gemm_launches_per_step, sec_per_launch, peaks, long_run)
 
     result = {
         "metric": "gemm_tflops",
@@ -496,48 +707,44 @@ def run_ours(args) -> dict:
         "warmup": args.warmup,
         "ms_per_step": ms_per_step,
         "higher_is_better": True,
-        "scaling": "strong" if workload in ("c5_nshard", "c5_kshard", "c5_kshard_fused") else "weak",
+        "scaling": "strong" if workload in SHARDED else "weak",
         "vs_baseline": None,
         "dtype": case.dtype,
         "data": "synthetic",
-        "config": {
-            "workload": f"{workload}: {case.dtype} '{case.layout}' M={case.m} N={case.n} K={case.k}"
-                        f"{' +bias' if case.bias_std is not None else ''} -> {case.out_dtype or case.dtype}",
+        "config": {"workload": workload_label(workload, case)},
+        "details": {
             "partition": w.partition,
             "l2": w.rotation,
             "launch": "CUDA graph of all timed steps" if replay is not None else "one host call per step",
-            "plan": {k: w.plan[k] for k in ("tile_m", "tile_n", "tile_k", "stages", "split_k", "swap_ab", "group_m", "grid",
-                                           "num_units", "stream_k", "sk_tiles", "a_repacked", "b_repacked")},
+            "plan": {k: w.plan[k] for k in PLAN_KEYS},
         },
         "roofline": roofline,
         "clocks": clocks.summary(),
         "gpu_launches": w.launches_per_step * args.steps,
         "e2e": e2e,
     }
+    if sustained is not None:
+        result["sustained"] = sustained
     result.update(w.extra)
+    del w, replay
+    gc.collect()
+    torch.cuda.empty_cache()
 
-    if world > 1 and workload == "c5_nshard":
-        # The same GEMM, whole, on one GPU (rank 0; the other ranks idle at the barrier): the denominator for scaling
-        # efficiency of this workload, measured in the same run under the same conditions.
-        single = None
-        if rank == 0:
-            del w
-            torch.cuda.empty_cache()
-            w1 = Workload("c5", args, 1, 0, device)
-            w1.step()
-            for _ in range(2):
-                w1.step()
-            ms1 = timed(stream, device, w1.step, max(3, min(args.steps, 10)), 1)
-            check_status(device)
-            single = {"value": w1.total_flops / (ms1 * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms1,
-                      "workload": "c5: the whole GEMM on one GPU (rank 0), timed after the sharded run"}
-            result["single_gpu_same_workload"] = single  # the denominator for a scaling figure; the ratio is left to the reader
-        dist.barrier()
+    if default_run and world == 1 and not args.no_configs:
+        # the small configurations of the benchmark list, one after the other on this GPU
+        result["configs"] = {name: small_config_record(name, args, device, stream, local, peaks) for name in SMALL_CONFIGS}
+    if default_run and world > 1 and not args.no_kshard:
+        for mode, key in (("c5_kshard", "kshard"), ("c5_kshard_fused", "kshard_fused")):
+            rec = kshard_record(mode, args, world, rank, local, device, stream, peaks)
+            if rank == 0:
+                result[key] = rec
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_reference_run(case)
+    if cpu is not None:
         result["cpu_baseline"] = {"value": cpu["tflops"], "unit": "TFLOP/s", "cores": cpu["cores"], "kind": "port",
                                   "sample": cpu["sample"], "host_cpu_count": cpu["cpu_count"]}
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
     return result if rank == 0 else None
 
@@ -549,7 +756,7 @@ def run_reference(args) -> dict | None:
     if rank != 0:
         return None
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    workload = args.workload or ("c2" if world == 1 else "c5_nshard")
+    workload = args.workload or ("c5" if world == 1 else "c5_nshard")
     case = O.CONFIGS["c5" if workload.startswith("c5") else workload]
     # each step is a bounded sample: a slab of rows sized so the whole run stays within a few minutes
     per_step_budget = max(1.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
@@ -570,15 +777,15 @@ def run_reference(args) -> dict | None:
         "warmup": args.warmup,
         "ms_per_step": statistics.median(r["full_pass_seconds_est"] for r in runs) * 1e3,
         "higher_is_better": True,
-        "scaling": "strong" if workload in ("c5_nshard", "c5_kshard", "c5_kshard_fused") else "weak",
+        "scaling": "strong" if workload in SHARDED else "weak",
         "vs_baseline": None,
         "dtype": case.dtype,
         "data": "synthetic",
-        "config": {"workload": f"{workload}: {case.dtype} '{case.layout}' M={case.m} N={case.n} K={case.k}"
-                               f"{' +bias' if case.bias_std is not None else ''} -> {case.out_dtype or case.dtype}",
-                   "note": "CPU torch.matmul fp32 (+bias): the ground truth of the reference's own tests; the reference kernel "
-                           "itself needs FlyDSL + an AMD gfx950 GPU and cannot run on this machine"},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": best["cores"], "kind": "port", "sample": best["sample"]},
+        "config": {"workload": workload_label(workload, case)},
+        "details": {"note": "CPU torch.matmul fp32 (+bias): the ground truth of the reference's own tests; the reference kernel "
+                            "itself needs FlyDSL + an AMD gfx950 GPU and cannot run on this machine"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": best["cores"], "kind": "port", "sample": best["sample"],
+                         "host_cpu_count": best["cpu_count"]},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -594,11 +801,13 @@ def main() -> None:
     ap.add_argument("--chunks", type=int, default=4)
     ap.add_argument("--policy", default=None, help="JSON dict of user_kwargs overriding the workload's policy")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--e2e-large", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the records of the small configurations (N = 1)")
+    ap.add_argument("--no-kshard", action="store_true", help="skip the K-sharded modes (N > 1)")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the loop of more than a second")
     ap.add_argument("--graph", default="auto", choices=("auto", "on", "off"))
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    workload = args.workload or ("c2" if world == 1 else "c5_nshard")
+    workload = args.workload or ("c5" if world == 1 else "c5_nshard")
     big = workload.startswith("c5")
     if args.impl == "reference":
         args.steps = args.steps if args.steps is not None else 3

@@ -14,6 +14,7 @@ from . import build as _build
 
 DTYPE_FP32, DTYPE_BF16, DTYPE_FP16 = 1, 2, 3
 STATIC_SCRATCH_BYTES = 16 << 20  # B200_GEMM_STATIC_SCRATCH_BYTES
+COUNTER_BYTES = 1 << 20          # B200_GEMM_COUNTER_BYTES: ticket region at the start of a workspace
 
 ERR_TEXT_FALLBACK = "b200_gemm error"
 
@@ -31,7 +32,8 @@ class Policy(C.Structure):
         ("stream_k", C.c_int32),
         ("no_pdl", C.c_int32),
         ("tile_k", C.c_int32),
-        ("reserved", C.c_int32 * 5),
+        ("wait_limit_us", C.c_int32),
+        ("reserved", C.c_int32 * 4),
     ]
 
 
@@ -119,6 +121,7 @@ EXPORTS = (
     "b200_peer_open",
     "b200_peer_close",
     "b200_gemm_selftest",
+    "b200_gemm_wait_selftest",
     "b200_gemm_strerror",
     "b200_gemm_version",
 )
@@ -180,6 +183,8 @@ def load() -> C.CDLL:
     lib.b200_peer_close.restype = C.c_int
     lib.b200_gemm_selftest.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
     lib.b200_gemm_selftest.restype = C.c_int
+    lib.b200_gemm_wait_selftest.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p]
+    lib.b200_gemm_wait_selftest.restype = C.c_int
     lib.b200_gemm_strerror.argtypes = [C.c_int]
     lib.b200_gemm_strerror.restype = C.c_char_p
     lib.b200_gemm_version.argtypes = []

@@ -446,6 +446,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   p.idesc = make_idesc(a->in_dtype, r.u_mn, r.v_mn, pl.tile_m, pl.tile_n);
   make_desc(r.u_mn, &p.u_desc_hi, &p.u_desc_lo, &p.u_kstep);
   make_desc(r.v_mn, &p.v_desc_hi, &p.v_desc_lo, &p.v_kstep);
+  p.wait_limit_ns = a->policy.wait_limit_us > 0 ? (unsigned long long)a->policy.wait_limit_us * 1000ull : kWaitLimitNs;
 
   const Variant* var = find_variant(pl.tile_n, pl.cta_group, pl.tile_k);
   const int vi = (int)(var - kVariants);
@@ -778,6 +779,14 @@ int b200_peer_open(const b200_peer_handle* handle, void** ptr) {
 int b200_peer_close(void* ptr, const b200_peer_handle* handle) {
   if (ptr == nullptr || handle == nullptr) return B200_GEMM_ERR_BAD_ARG;
   cudaError_t e = cudaIpcCloseMemHandle(static_cast<char*>(ptr) - handle->offset);
+  if (e != cudaSuccess) return b200::set_cuda_error(e);
+  return 0;
+}
+
+int b200_gemm_wait_selftest(int32_t* status, uint32_t limit_us, void* cuda_stream) {
+  if (status == nullptr || limit_us == 0 || limit_us > 1000000u) return B200_GEMM_ERR_BAD_ARG;
+  b200::wait_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(status, (unsigned long long)limit_us * 1000ull);
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return b200::set_cuda_error(e);
   return 0;
 }

@@ -61,6 +61,7 @@ struct alignas(64) GemmParams {
   uint32_t u_desc_hi, u_desc_lo;  // smem matrix descriptor without the start address
   uint32_t v_desc_hi, v_desc_lo;
   uint32_t u_kstep, v_kstep;  // start-address increment (16-byte units) per K=16 MMA inside a stage
+  unsigned long long wait_limit_ns;  // time limit of every wait inside the kernel
 };
 
 // One piece of work of a CTA: K blocks kb0, kb0+kstep, ... (kbn of them) of output tile (tp, tq). When `partial`, the fp32 result goes to
@@ -179,7 +180,7 @@ struct SmemLayout {
   static constexpr int kOutBytes = kRecvBytes > kStagingBytes ? kRecvBytes : kStagingBytes;
   static constexpr int kBiasOff = kOutOff + kOutBytes;   // float[256]
   static constexpr int kBarOff = kBiasOff + 256 * 4;     // full[S], empty[S], acc_full[2], acc_empty[2]
-  static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;  // tmem ptr, abort flag, last flag
+  static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;  // tmem ptr, abort flag, last flag, epilogue verdict
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynBytes = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
@@ -302,6 +303,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
   volatile uint32_t* tmem_ptr_s = reinterpret_cast<volatile uint32_t*>(sm + L::kMiscOff);
   volatile int* abort_s = reinterpret_cast<volatile int*>(sm + L::kMiscOff + 4);
   volatile int* last_s = reinterpret_cast<volatile int*>(sm + L::kMiscOff + 8);
+  volatile int* epi_abort_s = reinterpret_cast<volatile int*>(sm + L::kMiscOff + 12);
+  const unsigned long long wait_limit = p.wait_limit_ns;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -320,6 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
     }
     *abort_s = 0;
     *last_s = 0;
+    *epi_abort_s = 0;
     fence_mbar_init();
     prefetch_tmap(&p.tmap_u);
     prefetch_tmap(&p.tmap_v);
@@ -366,16 +370,59 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       wi.init(p, walker, walkers);
       Unit w;
       int item = 0;
+      // Requests of one K block: the U boxes and the V boxes of stage `st`, counted on barrier `fb`.
+      auto load = [&](uint32_t dst, const void* map, int x, int y, uint32_t fb) {
+        if constexpr (CG == 2)
+          tma_load_2d_pair(dst, map, x, y, fb);
+        else
+          tma_load_2d(dst, map, x, y, fb);
+      };
+      auto load_u = [&](int st, int kb, int p0, uint32_t fb) {
+        const uint32_t su = base + st * L::kStageBytes;
+#pragma unroll
+        for (int sub = 0; sub < L::kSub; ++sub) {
+          const int k0 = kb * TK + sub * kBoxK;
+          const uint32_t bu = su + sub * kUBoxBytes;
+          if (!p.u_mn_major) {
+            load(bu, &p.tmap_u, k0, p0, fb);
+          } else {
+            load(bu, &p.tmap_u, p0, k0, fb);
+            load(bu + 8192u, &p.tmap_u, p0 + 64, k0, fb);
+          }
+        }
+      };
+      auto load_v = [&](int st, int kb, int q0, uint32_t fb) {
+        const uint32_t sv = base + st * L::kStageBytes + L::kUStageBytes;
+#pragma unroll
+        for (int sub = 0; sub < L::kSub; ++sub) {
+          const int k0 = kb * TK + sub * kBoxK;
+          const uint32_t bv = sv + sub * L::kVBoxBytes;
+          if (!p.v_mn_major) {
+            load(bv, &p.tmap_v, k0, q0, fb);
+          } else {
+#pragma unroll
+            for (int j = 0; j < (kVRows >= 64 ? kVRows / 64 : 1); ++j) load(bv + 8192u * j, &p.tmap_v, q0 + 64 * j, k0, fb);
+          }
+        }
+      };
+      // Data of both CTAs of a pair is counted on the leader's barrier, which the MMA thread waits on.
+      auto full_target = [&](int st) {
+        uint32_t fb = full_bar(st);
+        if constexpr (CG == 2) fb = mapa_cluster(fb, 0);
+        return fb;
+      };
       // In the first pass over the ring every stage is free: no need to ask its barrier.
+#pragma unroll 1
       for (; ok && wi.next(p, w); ++item) {
         const int u = w.tile;
         const int p0 = (w.tp * CG + rank) * kTileP, q0 = w.tq * TILE_Q + rank * kVRows;
         if (lane == 0) trace_stamp(p, 0, item, 0);
+#pragma unroll 1
         for (int kj = 0; kj < w.kbn; ++kj) {
           const int kb = w.kb0 + kj * w.kstep;
           if (issued >= STAGES) {
             int good = 1;
-            if (lane == 0) good = mbar_wait<CG == 2>(empty_bar(stage), phase ^ 1u, abort_s) ? 1 : 0;
+            if (lane == 0) good = mbar_wait<CG == 2>(empty_bar(stage), phase ^ 1u, abort_s, wait_limit) ? 1 : 0;
             good = __shfl_sync(0xffffffffu, good, 0);
             if (!good) {
               if (lane == 0) report_abort(p, 0, u);
@@ -384,36 +431,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
             }
           }
           if (kj == 0 && lane == 0) trace_stamp(p, 0, item, 1);
-          // Data of both CTAs of a pair is counted on the leader's barrier, which the MMA thread waits on.
-          uint32_t fb = full_bar(stage);
-          if constexpr (CG == 2) fb = mapa_cluster(fb, 0);
-          const uint32_t su = base + stage * L::kStageBytes;
-          const uint32_t sv = su + L::kUStageBytes;
+          const uint32_t fb = full_target(stage);
           if (elect_one()) {
             if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), kTxBytes);
-            auto load = [&](uint32_t dst, const void* map, int x, int y) {
-              if constexpr (CG == 2)
-                tma_load_2d_pair(dst, map, x, y, fb);
-              else
-                tma_load_2d(dst, map, x, y, fb);
-            };
-#pragma unroll
-            for (int sub = 0; sub < L::kSub; ++sub) {
-              const int k0 = kb * TK + sub * kBoxK;
-              const uint32_t bu = su + sub * kUBoxBytes, bv = sv + sub * L::kVBoxBytes;
-              if (!p.u_mn_major) {
-                load(bu, &p.tmap_u, k0, p0);
-              } else {
-                load(bu, &p.tmap_u, p0, k0);
-                load(bu + 8192u, &p.tmap_u, p0 + 64, k0);
-              }
-              if (!p.v_mn_major) {
-                load(bv, &p.tmap_v, k0, q0);
-              } else {
-#pragma unroll
-                for (int j = 0; j < (kVRows >= 64 ? kVRows / 64 : 1); ++j) load(bv + 8192u * j, &p.tmap_v, q0 + 64 * j, k0);
-              }
-            }
+            load_u(stage, kb, p0, fb);
+            load_v(stage, kb, q0, fb);
           }
           __syncwarp();
           ++issued;
@@ -463,12 +485,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       // `ready` = the full barrier of the stage about to be consumed was already seen complete (probed one K block
       // ahead, so that the probe's latency hides behind the MMA issue of the block before).
       int ready = 0;
+#pragma unroll 1
       for (; ok && wi.next(p, w); ++it) {
         const int u = w.tile;
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         int good = 1;
-        if (lane == 0) good = mbar_wait<CG == 2>(acce_bar(buf), acc_phase ^ 1u, abort_s) ? 1 : 0;
+        if (lane == 0) good = mbar_wait<CG == 2>(acce_bar(buf), acc_phase ^ 1u, abort_s, wait_limit) ? 1 : 0;
         good = __shfl_sync(0xffffffffu, good, 0);
         if (!good) {
           if (lane == 0) report_abort(p, 1, u);
@@ -479,13 +502,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         int stalls = 0;
         long long c_wait = 0, c_mma = 0, c_commit = 0;
         const uint32_t d_tmem = tmem_base + buf * TILE_Q;
+#pragma unroll 1
         for (int kb = 0; kb < w.kbn; ++kb) {
           long long c0 = 0, c1 = 0, c3 = 0;
           if (tracing) c0 = clock64();
           if (!ready) {
             if (lane == 0) {
               ++stalls;
-              good = mbar_wait<CG == 2>(full_bar(stage), phase, abort_s) ? 1 : 0;
+              good = mbar_wait<CG == 2>(full_bar(stage), phase, abort_s, wait_limit) ? 1 : 0;
             }
             good = __shfl_sync(0xffffffffu, good, 0);
             if (!good) {
@@ -563,6 +587,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
     WorkIter wi;
     wi.init(p, walker, walkers);
     Unit w;
+#pragma unroll 1
     for (; wi.next(p, w); ++it) {
       const int u = w.tile;
       const int buf = it & 1;
@@ -586,10 +611,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         }
       }
 
-      if (!mbar_wait<CG == 2, false>(accf_bar(buf), acc_phase, abort_s)) {
+      // Every thread polls for itself (only the time limit ends its wait). A thread whose limit ran out says so in
+      // shared memory before it leaves; one that saw the barrier complete later finds that note and leaves too, so
+      // that either all 128 threads go on to the named barriers below or none does.
+      if (!mbar_wait<CG == 2, false>(accf_bar(buf), acc_phase, abort_s, wait_limit)) {
+        *epi_abort_s = 1;
         report_abort(p, 3, u);
         break;
       }
+      if (*epi_abort_s != 0) break;
       tc_fence_after();
       if (et == 0) {
         trace_stamp(p, 2, it, 0);
@@ -598,7 +628,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       const uint32_t t_acc = tmem_base + buf * TILE_Q + (uint32_t(quarter * 32) << 16);
       float4* part = nullptr;
       if (!direct) part = reinterpret_cast<float4*>(p.partials) + (size_t)(w.slot * CG + rank) * kSlotVec + row;
-
       // Two register buffers: the tcgen05.ld of chunk c+1 is in flight while chunk c is converted and stored.
       auto load_chunk = [&](uint32_t(&r)[32], int c) {
         if constexpr (CW == 32)
@@ -940,6 +969,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
     __syncwarp();
     tc_fence_after();
     tmem_dealloc<CG>(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// The bounded wait on its own: one thread waits on a barrier that nobody signals; the wait gives up after
+// `limit_ns` and the thread reports it in the 4-word status block like the GEMM roles do (role 9 = this test).
+__global__ void wait_selftest_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+    const bool completed = mbar_wait(smem_u32(&bar), 0u, &abort_flag, limit_ns);
+    if (!completed && atomicCAS(status, 0, 1) == 0) {
+      status[1] = (int)blockIdx.x;
+      status[2] = 9;
+      status[3] = -1;
+    }
   }
 }
 

@@ -1,7 +1,8 @@
 // Inline-PTX wrappers for the sm_100a features the A16W16 GEMM uses:
 // mbarrier, TMA (cp.async.bulk.tensor), tcgen05 (MMA, TMEM alloc/ld, commit, fences).
-// Every spin-wait here is bounded: after `kWaitLimitNs` it raises the CTA-wide abort flag and
-// returns false so the kernel can unwind (free TMEM, return an error status) instead of hanging.
+// Every spin-wait here is bounded: after its time limit (a kernel argument; `kWaitLimitNs` by default) it raises
+// the CTA-wide abort flag and returns false so the kernel can unwind (free TMEM, return an error status) instead
+// of hanging.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -80,22 +81,35 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 // Returns false when the wait was abandoned (limit hit, or another role aborted).
 // With kPollAbort == false only the time limit ends the wait, so that all threads waiting on one barrier
 // reach the same verdict (used where the waiters meet at a named barrier afterwards).
+// The limit is counted with the SM's cycle counter (cheap to read, unlike %globaltimer, which a spinning thread
+// must not read often): `limit_ns` nanoseconds are taken as 2 cycles each, i.e. the wait ends after limit_ns at
+// 2 GHz and proportionally later at lower clocks.
 template <bool kCluster = false, bool kPollAbort = true>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   auto probe = [&]() { return kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
   if (probe()) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  const long long t0 = clock64();
+  const long long limit_cycles = (long long)(limit_ns * 2ull);
   uint32_t it = 0;
   while (!probe()) {
-    if ((++it & 0xffu) == 0) {
+    if ((++it & 0x3fu) == 0) {
       if (kPollAbort && *abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
         return false;
       }
     }
   }
   return true;
+}
+
+// Acquire load of a 32-bit word in global memory (device scope): what it returns was written before every write the
+// writer released ahead of it.
+__device__ __forceinline__ int ld_acquire_gpu(const int* ptr) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
 }
 
 // ---------------------------------------------------------------- TMA

@@ -219,6 +219,7 @@ def _fill_args(a, b, out, bias, pol: _policy.Policy, a_t: bool, b_t: bool) -> _l
     p.stream_k = 1 if pol.stream_k else 0
     p.no_pdl = 0 if pol.pdl else 1
     p.tile_k = pol.tile_k
+    p.wait_limit_us = pol.wait_limit_us
     return args
 
 
@@ -240,7 +241,7 @@ def _call_key(a, b, out, bias, kw_key, stream_ptr, layout, out_dtype):
     return (
         a.data_ptr(), a.shape, a.stride(), a.dtype,
         b.data_ptr(), b.shape, b.stride(),
-        out.data_ptr(), out.shape, out.dtype,
+        out.data_ptr(), out.shape, out.stride(), out.dtype,
         None if bias is None else (bias.data_ptr(), bias.shape, bias.stride(), bias.dtype),
         kw_key, stream_ptr, layout, out_dtype, a.device.index, b.dtype, b.device.index, out.device.index,
     )
@@ -292,13 +293,18 @@ def gemm_a16w16(
         stream_ptr = (torch.cuda.current_stream(a.device) if stream is None else stream).cuda_stream
         kw_key = tuple(sorted(user_kwargs.items())) if user_kwargs else ()
         key = _call_key(a, b, out, bias, kw_key, stream_ptr, layout, out_dtype)
-        ent = _prepared.get(key)
-        if ent is not None and ent.ws_gen == ent.ws.generation:
-            if torch.cuda.current_device() == ent.dev:
-                rc = _lib.load().b200_gemm_launch(ent.handle, stream_ptr)
-            else:
-                with torch.cuda.device(ent.dev):
+        # The lock is held from the lookup to the end of the launch: a handle is released only after it has left the
+        # table under the same lock, so none can be freed while a launch is reading it.
+        with _prepared_lock:
+            ent = _prepared.get(key)
+            hit = ent is not None and ent.ws_gen == ent.ws.generation
+            if hit:
+                if torch.cuda.current_device() == ent.dev:
                     rc = _lib.load().b200_gemm_launch(ent.handle, stream_ptr)
+                else:
+                    with torch.cuda.device(ent.dev):
+                        rc = _lib.load().b200_gemm_launch(ent.handle, stream_ptr)
+        if hit:
             if rc != 0:
                 raise RuntimeError(f"b200_gemm_launch failed ({rc}): {_lib.strerror(rc)}")
             return out.view(-1, ent.n)
@@ -413,36 +419,42 @@ def gemm_a16w16_to_pointer(a: torch.Tensor, b: torch.Tensor, out_ptr: int, out_d
     key = ("ptr", a.data_ptr(), a.shape, a.stride(), a.dtype, b.data_ptr(), b.shape, b.stride(), out_ptr, out_dtype,
            kw_key, stream.cuda_stream, layout, device.index)
     lib = _lib.load()
-    ent = _prepared.get(key)
     dev_index = device.index if device.index is not None else torch.cuda.current_device()
-    if ent is None or ent.ws_gen != ent.ws.generation:
-        a_t, b_t = layout[0] == "t", layout[1] == "t"
-        m, k = a.shape
-        n = b.shape[1]
-        assert b.shape[0] == k and m > 0 and n > 0 and k > 0
-        _check_operand("A", a, a_t, False, m)
-        _check_operand("B", b, b_t, False, None)
-        pol = resolve_policy(m, n, k, a.dtype, layout, user_kwargs, _num_sms(device))
-        why = _policy.validate(pol, m, n, k, layout)
-        assert why is None, f"unsupported gemm_a16w16 shape/config: {why}"
-        args = _fill_args(a, b, torch.empty(0, dtype=out_dtype), None, pol, a_t, b_t)
-        args.out = out_ptr
-        ws = _workspace_for(device, stream)
-        with torch.cuda.device(dev_index):
-            need = lib.b200_gemm_workspace_bytes(C.byref(args))
-            if need:
-                ws.ensure(need, device, stream)
-                args.workspace = ws.buf.data_ptr()
-                args.workspace_bytes = ws.buf.numel()
-            args.status = ws.status.data_ptr()
-            handle = C.c_void_p()
-            rc = lib.b200_gemm_prepare(C.byref(args), C.byref(handle))
-        if rc != 0:
-            raise RuntimeError(f"b200_gemm_prepare failed ({rc}): {_lib.strerror(rc)}")
-        ent = _Prepared(handle, ws, dev_index, n)
-        _remember(key, ent)
+    with _prepared_lock:  # held across lookup and launch, see gemm_a16w16
+        ent = _prepared.get(key)
+        if ent is not None and ent.ws_gen == ent.ws.generation:
+            with torch.cuda.device(ent.dev):
+                rc = lib.b200_gemm_launch(ent.handle, C.c_void_p(stream.cuda_stream))
+            if rc != 0:
+                raise RuntimeError(f"b200_gemm_launch failed ({rc}): {_lib.strerror(rc)}")
+            return
+    a_t, b_t = layout[0] == "t", layout[1] == "t"
+    m, k = a.shape
+    n = b.shape[1]
+    assert b.shape[0] == k and m > 0 and n > 0 and k > 0
+    _check_operand("A", a, a_t, False, m)
+    _check_operand("B", b, b_t, False, None)
+    pol = resolve_policy(m, n, k, a.dtype, layout, user_kwargs, _num_sms(device))
+    why = _policy.validate(pol, m, n, k, layout)
+    assert why is None, f"unsupported gemm_a16w16 shape/config: {why}"
+    args = _fill_args(a, b, torch.empty(0, dtype=out_dtype), None, pol, a_t, b_t)
+    args.out = out_ptr
+    ws = _workspace_for(device, stream)
+    with torch.cuda.device(dev_index):
+        need = lib.b200_gemm_workspace_bytes(C.byref(args))
+        if need:
+            ws.ensure(need, device, stream)
+            args.workspace = ws.buf.data_ptr()
+            args.workspace_bytes = ws.buf.numel()
+        args.status = ws.status.data_ptr()
+        handle = C.c_void_p()
+        rc = lib.b200_gemm_prepare(C.byref(args), C.byref(handle))
+    if rc != 0:
+        raise RuntimeError(f"b200_gemm_prepare failed ({rc}): {_lib.strerror(rc)}")
+    ent = _Prepared(handle, ws, dev_index, n)
     with torch.cuda.device(ent.dev):
         rc = lib.b200_gemm_launch(ent.handle, C.c_void_p(stream.cuda_stream))
+    _remember(key, ent)  # only now can another thread find (and, by eviction, release) the handle
     if rc != 0:
         raise RuntimeError(f"b200_gemm_launch failed ({rc}): {_lib.strerror(rc)}")
 
@@ -475,5 +487,11 @@ def check_status(device: Optional[torch.device] = None) -> None:
             continue
         st = ws.status.tolist()
         if st[0] != 0:
+            # A kernel that gave up may have left split-K / stream-K tickets taken: the next call on this workspace
+            # would elect the wrong last arriver. Clear them, and forget every resolved launch.
             ws.status.zero_()
+            if ws.buf is not None:
+                ws.buf[: _lib.COUNTER_BYTES].zero_()
+            torch.cuda.synchronize(ws.status.device)
+            clear_prepared_calls()
             raise RuntimeError(f"b200 gemm kernel gave up a bounded wait: code={st[0]} cta={st[1]} role={st[2]} unit={st[3]}")

@@ -47,7 +47,7 @@ REFERENCE_KEYS = (
 # Keys that only exist here.
 BLACKWELL_KEYS = ("tile_n", "swap_ab", "cta_group", "split_mode", "max_ctas", "stream_k", "tile_k")
 # Keys that switch behaviour without describing a tiling (they do not make a dict a "Blackwell policy").
-CONTROL_KEYS = ("strict_reference_envelope", "pdl")
+CONTROL_KEYS = ("strict_reference_envelope", "pdl", "wait_limit_us")
 SPLIT_MODES = {"ticket": 0, "cluster": 2}
 
 
@@ -64,6 +64,7 @@ class Policy:
     stream_k: bool = False
     pdl: bool = True         # programmatic dependent launch: set-up overlaps the previous kernel in the stream
     tile_k: int = 0          # K elements per pipeline stage; 0 = the tile's default (see tile_k())
+    wait_limit_us: int = 0   # time limit of the kernel's waits in microseconds; 0 = 2 s
 
     def as_dict(self) -> dict:
         return asdict(self)
@@ -167,6 +168,8 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
         return f"split_mode must be one of {tuple(SPLIT_MODES)}, got {pol.split_mode!r}"
     if pol.group_m < 0:
         return f"group_m must be >= 0, got {pol.group_m}"
+    if pol.wait_limit_us < 0:
+        return f"wait_limit_us must be >= 0, got {pol.wait_limit_us}"
     if pol.split_mode == "cluster" and pol.split_k > 1 and (pol.cta_group != 1 or pol.stream_k):
         return "cluster split-K needs cta_group 1 and no stream_k"
     if pol.split_mode == "cluster" and pol.split_k > 1 and pol.tile_n > 64:
@@ -279,11 +282,13 @@ def from_user_kwargs(user_kwargs: dict, m: int, n: int, k: int, layout: str, num
             fields["split_k"] = int(user_kwargs["split_k"])
         if "group_m" in user_kwargs:
             fields["group_m"] = int(user_kwargs["group_m"])
-    if "pdl" in user_kwargs:
-        fields["pdl"] = user_kwargs["pdl"]
+    for key in ("pdl", "wait_limit_us"):
+        if key in user_kwargs:
+            fields[key] = user_kwargs[key]
     fields["swap_ab"] = bool(fields["swap_ab"])
     fields["stream_k"] = bool(fields["stream_k"])
     fields["pdl"] = bool(fields["pdl"])
+    fields["wait_limit_us"] = int(fields["wait_limit_us"])
     pol = Policy(**fields)
     return pol
 

@@ -63,7 +63,9 @@ typedef struct b200_gemm_policy {
                          waits for that kernel to complete before it reads or writes global memory               */
   int32_t tile_k;     /* K elements per pipeline stage: 64 or 128 where the variant table has both (single-CTA tiles up
                          to 128 wide); 0 = the tile's default (128 there, 64 for 256-wide tiles and CTA pairs)      */
-  int32_t reserved[5];
+  int32_t wait_limit_us; /* time limit of every wait inside the kernel, in microseconds; 0 = 2 seconds. A wait that
+                            runs out makes the kernel give up, free what it holds and report through `status`       */
+  int32_t reserved[4];
 } b200_gemm_policy;
 
 /* One GEMM call. Replaces the argument list of the reference's jit host stub gemm_a16w16_gfx950
@@ -84,7 +86,9 @@ typedef struct b200_gemm_args {
   b200_gemm_policy policy;
   void* workspace; /* device scratch of at least b200_gemm_workspace_bytes(), 256-byte aligned; its first
                       B200_GEMM_COUNTER_BYTES hold the split-K / stream-K tickets: zero them once before the first
-                      call; every call leaves them zero again (self-cleaning)                                   */
+                      call; every call that completes leaves them zero again (self-cleaning). A call that reported
+                      a given-up wait through `status` may leave tickets behind: zero the region again before the
+                      next call that uses this workspace                                                         */
   uint64_t workspace_bytes;
   int32_t* status; /* device int32[4], or NULL. Written only when a bounded wait inside a kernel gave up:
                       [0]=error code (1), [1]=CTA, [2]=role, [3]=unit                                         */
@@ -206,6 +210,14 @@ int b200_peer_close(void* ptr, const b200_peer_handle* handle);
  * built-in scratch. The reference has no counterpart: its descriptors are generated by FlyDSL
  * (kernels/gemm_a16w16_gfx950.py:378-705 are traced, not hand-encoded). */
 int b200_gemm_selftest(void* cuda_stream, int32_t* failed_case);
+
+/* Check of the bounded-wait mechanism every kernel of this library relies on, without running a GEMM: launches one
+ * thread that waits on a shared-memory barrier nobody ever signals, with a limit of `limit_us` microseconds (1 ...
+ * 1000000). The wait runs out, and the thread reports it exactly as a GEMM kernel would: status[0] = 1, status[1] = 0
+ * (CTA), status[2] = 9 (role: self-test), status[3] = -1; then the kernel returns normally and the context stays
+ * usable. `status` is a device int32[4] that the caller zeroed. Takes the place of the unbounded flag spin of the
+ * reference's split-K protocol (kernels/gemm_a16w16_gfx950_utils.py:216-247), which has no such exit. */
+int b200_gemm_wait_selftest(int32_t* status, uint32_t limit_us, void* cuda_stream);
 
 /* Text for an error code; for B200_GEMM_ERR_LAUNCH the last CUDA error string seen by this thread. */
 const char* b200_gemm_strerror(int code);

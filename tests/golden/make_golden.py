@@ -1,8 +1,8 @@
 """Generate tests/golden/ref_func_cases.npz from the reference's own test oracle.
 
-Run in a container that has the reference checkout (it does not travel to the GPU box):
+Run where a checkout of xytpai/flydsl-examples is at hand (it does not travel to the GPU box), passing its path:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the flydsl-examples checkout>
 
 The reference's test module (test_gemm_a16w16_gfx950.py) is loaded by file path; its `from kernels... import`
 lines resolve to this repository's drop-in `kernels` package, so the module imports without FlyDSL. Its
@@ -44,7 +44,9 @@ def load_reference_test_module(ref_root: Path):
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path to the flydsl-examples checkout>")
+    ref_root = Path(sys.argv[1])
     mod = load_reference_test_module(ref_root)
     dts = {"bf16": torch.bfloat16, "fp16": torch.float16}
     blob = {}

@@ -22,9 +22,7 @@ def test_every_declared_symbol_is_exported():
     assert "b200_gemm_a16w16" in declared and len(declared) >= 7
     for name in declared:
         assert getattr(lib, name) is not None, name
-    assert declared == set(_lib.EXPORTS) | {n for n in declared if n not in _lib.EXPORTS}
-    for name in _lib.EXPORTS:
-        assert name in declared, f"{name} is bound but not declared in include/"
+    assert declared == set(_lib.EXPORTS), (sorted(declared - set(_lib.EXPORTS)), sorted(set(_lib.EXPORTS) - declared))
 
 
 def test_version_variants_and_strerror():
@@ -87,3 +85,10 @@ def test_multi_gpu_entry_points_validate_before_touching_a_device():
     assert call(odt=7) == -1
     assert call(bias=C.c_void_p(64), bdt=1) == -1  # bias must be bf16 or fp16
     assert call(rows=0) == 0               # nothing to do is not an error
+
+
+def test_wait_selftest_validates_its_arguments():
+    lib = _lib.load()
+    assert lib.b200_gemm_wait_selftest(None, 100, None) == -1
+    assert lib.b200_gemm_wait_selftest(C.c_void_p(4096), 0, None) == -1         # no limit given
+    assert lib.b200_gemm_wait_selftest(C.c_void_p(4096), 2_000_000, None) == -1  # beyond one second

@@ -573,3 +573,36 @@ def test_linearity_at_full_config2_size():
     rhs = f(a1) + f(a2)
     check_status()
     assert torch.equal(lhs, rhs)
+
+
+def test_bounded_wait_runs_out_and_is_reported():
+    """The liveness guarantee of every kernel here: a wait that nobody satisfies ends at its time limit, the kernel
+    returns normally with a note in the status block, and the context stays usable. Exercised on the wait primitive
+    alone (one thread, one barrier nobody signals, 200 us limit): no GEMM is made to fail."""
+    import ctypes as C
+
+    from flydsl_examples_b200 import _lib
+    from flydsl_examples_b200 import gemm_a16w16 as G
+
+    lib = _lib.load()
+    # a split-K call first, so that this stream has a workspace whose tickets check_status() must clear
+    case = O.Case("before", "bf16", "nt", 200, 328, 1000, seed=77, bias_std=0.5, user_kwargs={"tile_n": 64, "split_k": 3})
+    run_case(case)
+    stream = torch.cuda.current_stream()
+    ws = G._workspace_for(torch.device("cuda", torch.cuda.current_device()), stream)
+    ws.buf[:64].fill_(7)  # tickets as a kernel that gave up could have left them
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    rc = lib.b200_gemm_wait_selftest(ws.status.data_ptr(), 200, C.c_void_p(stream.cuda_stream))
+    t1.record()
+    assert rc == 0, _lib.strerror(rc)
+    torch.cuda.synchronize()
+    assert t0.elapsed_time(t1) < 50.0  # milliseconds: the limit ended the wait (200 us at 2 GHz; longer at low clocks)
+    assert ws.status.tolist() == [1, 0, 9, -1]
+    with pytest.raises(RuntimeError, match="gave up a bounded wait: code=1 cta=0 role=9"):
+        check_status()
+    assert ws.status.tolist() == [0, 0, 0, 0] or ws.status.tolist()[0] == 0
+    assert int(ws.buf[:64].sum()) == 0  # the ticket region was cleared
+    check_status()                      # nothing pending any more
+    run_case(case, repeats=2)           # and the next split-K call on this stream is right

@@ -263,3 +263,31 @@ def test_stream_k_plan_matches_the_library():
         assert pl["stream_k"] == (1 if sk_tiles else 0)
         if sk_tiles:
             assert pl["partial_bytes"] == sk_tiles * sk_slots * 128 * tile_n * 4 and pl["counter_bytes"] == 1 << 20
+
+
+def test_call_key_tells_output_strides_apart():
+    # A prepared launch is reused only for an identical call. Two outputs with the same address, shape and dtype but
+    # different strides are different calls: the second one must reach the `out.is_contiguous()` assertion
+    # (kernels/gemm_a16w16_gfx950.py:1381) instead of hitting the cache.
+    from flydsl_examples_b200 import gemm_a16w16 as G
+
+    a = torch.empty(8, 16, dtype=torch.bfloat16)
+    b = torch.empty(4, 16, dtype=torch.bfloat16).t()
+    big = torch.empty(8, 8, dtype=torch.bfloat16)
+    contiguous = big.view(-1)[:32].view(8, 4)
+    strided = big[:, :4]
+    assert contiguous.data_ptr() == strided.data_ptr() and contiguous.shape == strided.shape
+    key1 = G._call_key(a, b, contiguous, None, (), 0, "nt", None)
+    key2 = G._call_key(a, b, strided, None, (), 0, "nt", None)
+    assert key1 != key2
+    with pytest.raises(AssertionError):
+        G.gemm_a16w16(a, b, strided, layout="nt")
+
+
+def test_wait_limit_is_a_control_key():
+    # it rides along with a tuned or heuristic tiling instead of replacing it
+    pol = P.from_user_kwargs({"wait_limit_us": 50}, 2048, 4096, 4096, "nt")
+    base = P.from_user_kwargs({}, 2048, 4096, 4096, "nt")
+    assert pol.wait_limit_us == 50 and base.wait_limit_us == 0
+    assert (pol.tile_n, pol.cta_group, pol.split_k) == (base.tile_n, base.cta_group, base.split_k)
+    assert P.validate(P.Policy(tile_n=64, wait_limit_us=-1), 64, 64, 64, "nt") is not None
