@@ -33,7 +33,8 @@ class Policy(C.Structure):
         ("no_pdl", C.c_int32),
         ("tile_k", C.c_int32),
         ("wait_limit_us", C.c_int32),
-        ("reserved", C.c_int32 * 4),
+        ("loader", C.c_int32),
+        ("reserved", C.c_int32 * 3),
     ]
 
 
@@ -84,6 +85,8 @@ class Plan(C.Structure):
         ("sk_slots", C.c_int32),
         ("a_repacked", C.c_int32),
         ("b_repacked", C.c_int32),
+        ("a_loader", C.c_int32),
+        ("b_loader", C.c_int32),
         ("counter_bytes", C.c_uint64),
         ("partial_bytes", C.c_uint64),
         ("repack_bytes", C.c_uint64),

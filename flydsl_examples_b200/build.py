@@ -20,13 +20,15 @@ INCLUDE = PKG_DIR.parent / "include"
 LIB_PATH = PKG_DIR / "libb200_gemm.so"
 STAMP_PATH = PKG_DIR / "libb200_gemm.so.stamp"
 
-SOURCES = [CSRC / "gemm_api.cu"]
-HEADERS = [CSRC / "gemm_kernel.cuh", CSRC / "ptx.cuh", INCLUDE / "b200_gemm.h"]
+SOURCES = [CSRC / name for name in ("gemm_api.cu", "variants_single_k128.cu", "variants_single_k64.cu", "variants_pair.cu",
+                                    "variants_loader.cu")]
+HEADERS = [CSRC / "gemm_kernel.cuh", CSRC / "aux_kernels.cuh", CSRC / "variants.h", CSRC / "ptx.cuh", INCLUDE / "b200_gemm.h"]
+OBJ_DIR = PKG_DIR / "_obj"  # object files of the translation units (not shipped, not tracked)
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
-    "-shared", "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
 ]
 # Not used: --split-compile. With it the same sources came out with half as much code again per kernel (about 196 KB
@@ -54,19 +56,35 @@ def is_current() -> bool:
     return LIB_PATH.exists() and STAMP_PATH.exists() and STAMP_PATH.read_text().strip() == _source_digest()
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if the sources changed since the last build; return its path."""
-    if not force and is_current():
-        return LIB_PATH
-    cmd = [_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}"]
+def _compile_one(src: Path, verbose: bool) -> tuple[Path, str]:
+    obj = OBJ_DIR / (src.stem + ".o")
+    cmd = [_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}", "-c"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB_PATH), *map(str, SOURCES)]
+    cmd += ["-o", str(obj), str(src)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose:
-        sys.stderr.write(proc.stderr)
     if proc.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
+    return obj, proc.stderr
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile the library if the sources changed since the last build; return its path. The translation units are
+    compiled side by side (one nvcc process each), then linked into one shared object."""
+    if not force and is_current():
+        return LIB_PATH
+    from concurrent.futures import ThreadPoolExecutor
+
+    OBJ_DIR.mkdir(exist_ok=True)
+    with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+        results = list(pool.map(lambda src: _compile_one(src, verbose), SOURCES))
+    if verbose:
+        for _, log in results:
+            sys.stderr.write(log)
+    cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *[str(obj) for obj, _ in results]]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("link failed:\n" + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
     STAMP_PATH.write_text(_source_digest() + "\n")
     return LIB_PATH
 

@@ -9,11 +9,11 @@
 #include <new>
 
 #include "../../include/b200_gemm.h"
-#include "gemm_kernel.cuh"
+#include "aux_kernels.cuh"
+#include "variants.h"
 
 namespace b200 {
 
-constexpr int kSmemLimit = 232448;  // 227 KB opt-in dynamic shared memory per CTA on sm_100
 constexpr int kMaxDevices = 16;
 constexpr uint64_t kCounterBytes = 1u << 20;  // fixed ticket region at the start of the workspace (262144 tiles)
 
@@ -53,43 +53,22 @@ static GetAddressRangeFn get_address_range_fn() {
 static thread_local char g_last_cuda_error[256] = "";
 
 // ------------------------------------------------------------------ variant table
-typedef void (*KernelFn)(const GemmParams);
+// The kernels themselves are instantiated in variants_*.cu; this is the menu: (tile_n, CTAs per tile, K elements per
+// stage, deepest ring). The first entry of a (tile, cta_group) is the default when the policy leaves tile_k at 0.
 struct Variant {
   int tile_q, cta_group, tile_k, max_stages;
-  KernelFn fn[13];  // indexed by stage count (2..12)
 };
-
-template <int TILE_Q, int S, int CG, int TK>
-constexpr KernelFn kfn() {
-  if constexpr (SmemLayout<TILE_Q, S, CG, TK>::kDynBytes <= kSmemLimit)
-    return gemm_a16w16_sm100_kernel<TILE_Q, S, CG, TK>;
-  else
-    return nullptr;
-}
-
-// Stages of 64 K elements: every tile and CTA pair. Stages of 128 K elements: single-CTA tiles up to 128 wide (default there).
-#define B200_VARIANT_K64(TQ, CG, MAXS)                                                                            \
-  {                                                                                                               \
-    TQ, CG, 64, MAXS, {                                                                                           \
-      nullptr, nullptr, kfn<TQ, 2, CG, 64>(), kfn<TQ, 3, CG, 64>(), kfn<TQ, 4, CG, 64>(), kfn<TQ, 5, CG, 64>(),   \
-          kfn<TQ, 6, CG, 64>(), nullptr, kfn<TQ, 8, CG, 64>(), nullptr, nullptr, nullptr, nullptr                 \
-    }                                                                                                             \
-  }
-#define B200_VARIANT_K128(TQ, MAXS)                                                                               \
-  {                                                                                                               \
-    TQ, 1, 128, MAXS, {                                                                                           \
-      nullptr, nullptr, kfn<TQ, 2, 1, 128>(), kfn<TQ, 3, 1, 128>(), kfn<TQ, 4, 1, 128>(), kfn<TQ, 5, 1, 128>(),   \
-          nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr                                           \
-    }                                                                                                             \
-  }
-
 static const Variant kVariants[] = {
-    // The first entry of a (tile, cta_group) is the default when the policy leaves tile_k at 0.
-    B200_VARIANT_K128(16, 5),     B200_VARIANT_K128(32, 5),    B200_VARIANT_K128(64, 4),    B200_VARIANT_K128(128, 3),
-    B200_VARIANT_K64(256, 1, 4),  B200_VARIANT_K64(128, 2, 8), B200_VARIANT_K64(256, 2, 6),  B200_VARIANT_K64(192, 2, 6),
-    B200_VARIANT_K64(16, 1, 8),   B200_VARIANT_K64(32, 1, 8),  B200_VARIANT_K64(64, 1, 8),  B200_VARIANT_K64(128, 1, 6),
+    {16, 1, 128, 5}, {32, 1, 128, 5}, {64, 1, 128, 4}, {128, 1, 128, 3}, {256, 1, 64, 4}, {128, 2, 64, 8},
+    {256, 2, 64, 6}, {192, 2, 64, 6}, {16, 1, 64, 8},  {32, 1, 64, 8},   {64, 1, 64, 8},  {128, 1, 64, 6},
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
+constexpr int kMaxStages = 12;
+
+static KernelFn variant_fn(const Variant& v, int stages) {
+  if (v.cta_group == 2) return pair_variant(v.tile_q, stages);
+  return v.tile_k == 128 ? single_k128_variant(v.tile_q, stages) : single_k64_variant(v.tile_q, stages);
+}
 
 static const Variant* find_variant(int tile_q, int cta_group, int tile_k) {
   for (int i = 0; i < kNumVariants; ++i)
@@ -103,12 +82,12 @@ static int dyn_smem_bytes(int tile_q, int stages, int cta_group, int tile_k) {
   const int staging0 = tile_q >= 64 ? 4 * 2 * 32 * 128 : 0;
   const int recv = tile_q <= 64 ? kTileP * tile_q * 4 : 0;
   const int staging = recv > staging0 ? recv : staging0;
-  return stages * (kTileP * tile_k * 2 + (tile_q / cta_group) * tile_k * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024;
+  return stages * (kTileP * tile_k * 2 + (tile_q / cta_group) * tile_k * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 32 + 1024;
 }
 
 struct DeviceInfo {
   int sm_count = 0;
-  bool attr_set[kNumVariants][13] = {};
+  bool attr_set[kNumVariants][kMaxStages + 1][2] = {};  // [variant][stages][with loader warps]
 };
 static DeviceInfo g_dev[kMaxDevices];
 static std::mutex g_dev_mutex;
@@ -132,6 +111,11 @@ static inline uint64_t round_up(uint64_t x, uint64_t a) { return (x + a - 1) / a
 
 static bool tma_encodable(const void* ptr, int64_t ld) {
   return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && ((ld * 2) & 15) == 0;
+}
+// A K-contiguous operand whose rows start on 8-byte boundaries can be fetched by the loader warps (cp.async, 8 or 16
+// bytes per copy) when TMA cannot describe it.
+static bool loader_fetchable(const void* ptr, int64_t ld, int mn_major) {
+  return !mn_major && (reinterpret_cast<uintptr_t>(ptr) & 7) == 0 && ((ld * 2) & 7) == 0;
 }
 
 struct Resolved {
@@ -172,8 +156,13 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
   // A is K-major when 'n'; B[K,N] is K-major when 't'.
   const int a_mn = a->a_trans ? 1 : 0;
   const int b_mn = a->b_trans ? 0 : 1;
-  pl.a_repacked = tma_encodable(a->a, a->lda) ? 0 : 1;
-  pl.b_repacked = tma_encodable(a->b, a->ldb) ? 0 : 1;
+  // Operands TMA cannot describe are copied into an aligned image first; when the policy asks for it and their layout
+  // allows, the kernel's loader warps fetch them instead (no copy, no scratch, but far slower: see b200_gemm.h).
+  const bool loader_ok = pol.loader != 0 && loader_variant(pl.tile_n, pl.cta_group, var->tile_k, nullptr) != nullptr;
+  pl.a_loader = (!tma_encodable(a->a, a->lda) && loader_ok && loader_fetchable(a->a, a->lda, a_mn)) ? 1 : 0;
+  pl.b_loader = (!tma_encodable(a->b, a->ldb) && loader_ok && loader_fetchable(a->b, a->ldb, b_mn)) ? 1 : 0;
+  pl.a_repacked = (tma_encodable(a->a, a->lda) || pl.a_loader) ? 0 : 1;
+  pl.b_repacked = (tma_encodable(a->b, a->ldb) || pl.b_loader) ? 0 : 1;
   // Repacked images: K-major operand -> [rows, round_up(K,8)]; MN-major operand -> [K, round_up(rows,8)].
   const int64_t a_rows = a_mn ? a->k : a->m, a_cols = a_mn ? a->m : a->k;
   const int64_t b_rows = b_mn ? a->k : a->n, b_cols = b_mn ? a->n : a->k;
@@ -201,8 +190,9 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
 
   int stages = pol.stages;
   if (stages <= 0 || stages > var->max_stages) stages = var->max_stages;
-  while (stages >= 2 && (var->fn[stages] == nullptr)) --stages;
+  while (stages >= 2 && variant_fn(*var, stages) == nullptr) --stages;
   if (stages < 2) return B200_GEMM_ERR_BAD_POLICY;
+  if (pl.a_loader || pl.b_loader) loader_variant(pl.tile_n, pl.cta_group, var->tile_k, &stages);  // one depth is built
   pl.stages = stages;
   pl.smem_bytes = dyn_smem_bytes(pl.tile_n, stages, pl.cta_group, pl.tile_k);
   pl.tmem_cols = 32;
@@ -343,7 +333,7 @@ struct RepackJob {
 struct b200_gemm_handle {
   b200::GemmParams params;
   b200::KernelFn fn;
-  int grid, smem_bytes, device, cta_group, cluster_split, pdl;
+  int grid, threads, smem_bytes, device, cta_group, cluster_split, pdl;
   int n_repack;
   b200::RepackJob repack[2];
   b200_gemm_plan plan;
@@ -398,10 +388,19 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   const void* u_ptr = pl.swap_ab ? pb : pa;
   const void* v_ptr = pl.swap_ab ? pa : pb;
   const int64_t u_ld = pl.swap_ab ? ldb : lda, v_ld = pl.swap_ab ? lda : ldb;
-  rc = encode_operand(&p.tmap_u, u_ptr, a->in_dtype, r.u_mn, r.P, a->k, u_ld, kTileP);
-  if (rc) return rc;
-  rc = encode_operand(&p.tmap_v, v_ptr, a->in_dtype, r.v_mn, r.Q, a->k, v_ld, pl.tile_n / pl.cta_group);
-  if (rc) return rc;
+  const int u_cp = pl.swap_ab ? pl.b_loader : pl.a_loader, v_cp = pl.swap_ab ? pl.a_loader : pl.b_loader;
+  if (!u_cp) {
+    rc = encode_operand(&p.tmap_u, u_ptr, a->in_dtype, r.u_mn, r.P, a->k, u_ld, kTileP);
+    if (rc) return rc;
+  }
+  if (!v_cp) {
+    rc = encode_operand(&p.tmap_v, v_ptr, a->in_dtype, r.v_mn, r.Q, a->k, v_ld, pl.tile_n / pl.cta_group);
+    if (rc) return rc;
+  }
+  p.u_cp = u_cp, p.v_cp = v_cp;
+  p.u_src = u_ptr, p.v_src = v_ptr;
+  p.u_pitch = u_ld * 2, p.v_pitch = v_ld * 2;
+  p.tma_tx_bytes = (uint32_t)(pl.cta_group * pl.tile_k * 2 * ((u_cp ? 0 : kTileP) + (v_cp ? 0 : pl.tile_n / pl.cta_group)));
   p.out = a->out;
   p.bias = a->bias;
   {
@@ -450,7 +449,10 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
 
   const Variant* var = find_variant(pl.tile_n, pl.cta_group, pl.tile_k);
   const int vi = (int)(var - kVariants);
-  h->fn = var->fn[pl.stages];
+  const int with_loader = (u_cp || v_cp) ? 1 : 0;
+  h->fn = with_loader ? loader_variant(pl.tile_n, pl.cta_group, pl.tile_k, nullptr) : variant_fn(*var, pl.stages);
+  if (h->fn == nullptr) return B200_GEMM_ERR_BAD_POLICY;
+  h->threads = with_loader ? kThreadsLoader : kThreads;
   h->grid = pl.grid;
   h->smem_bytes = pl.smem_bytes;
   h->cta_group = pl.cta_group;
@@ -463,11 +465,11 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   }
   {
     std::lock_guard<std::mutex> lock(g_dev_mutex);
-    if (!dev->attr_set[vi][pl.stages]) {
+    if (!dev->attr_set[vi][pl.stages][with_loader]) {
       cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(h->fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            pl.smem_bytes);
       if (e != cudaSuccess) return set_cuda_error(e);
-      dev->attr_set[vi][pl.stages] = true;
+      dev->attr_set[vi][pl.stages][with_loader] = true;
     }
   }
   return 0;
@@ -485,7 +487,7 @@ static int run(const b200_gemm_handle* h, cudaStream_t stream) {
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(h->grid, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(h->threads, 1, 1);
   cfg.dynamicSmemBytes = h->smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -541,8 +543,15 @@ int b200_gemm_a16w16_static_scratch(const b200_gemm_args* args, void* cuda_strea
   b200_gemm_plan plan;
   int rc = b200_gemm_plan_query(args, &plan);
   if (rc) return rc;
-  if (plan.workspace_bytes > (uint64_t)B200_GEMM_STATIC_SCRATCH_BYTES) return B200_GEMM_ERR_TOO_LARGE;
   b200_gemm_args local = *args;
+  if (plan.workspace_bytes > (uint64_t)B200_GEMM_STATIC_SCRATCH_BYTES && (plan.a_repacked || plan.b_repacked) && !local.policy.loader) {
+    // The aligned copies of the operands do not fit the built-in array: let the kernel's loader warps fetch them
+    // where their layout allows (slower, but needs no scratch for them).
+    local.policy.loader = 1;
+    rc = b200_gemm_plan_query(&local, &plan);
+    if (rc) return rc;
+  }
+  if (plan.workspace_bytes > (uint64_t)B200_GEMM_STATIC_SCRATCH_BYTES) return B200_GEMM_ERR_TOO_LARGE;
   local.workspace = nullptr;
   local.workspace_bytes = 0;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);

@@ -7,7 +7,9 @@
 // host encodes the tensor map, how many 64-wide TMA boxes one stage takes, and two descriptor fields.
 //
 // Roles (192 threads): warp 0 = TMA producer (one elected lane), warp 1 = TMEM owner + MMA issuer (one lane),
-// warps 2..5 = epilogue (warp w owns TMEM lanes 32*(w%4)..+31). The accumulator is double-buffered in TMEM so the
+// warps 2..5 = epilogue (warp w owns TMEM lanes 32*(w%4)..+31). The LOADER variants have two more warps (6, 7)
+// that fetch K-contiguous operands TMA cannot describe (base or pitch not a multiple of 16 bytes) with per-thread
+// cp.async copies, writing the very 128-byte-swizzled image a TMA box would have left. The accumulator is double-buffered in TMEM so the
 // epilogue of one unit overlaps the main loop of the next. A work unit is (output tile, K-slice); CTA b walks
 // units b, b+grid, b+2*grid, ...
 //
@@ -28,6 +30,8 @@ constexpr int kBoxK = 64;    // K elements per TMA box = one 128-byte swizzle sp
 constexpr int kUmmaK = 16;   // K elements per tcgen05.mma kind::f16
 constexpr int kThreads = 192;
 constexpr int kEpiThreads = 128;
+constexpr int kLoaderThreads = 64;                       // warps 6 and 7 of a LOADER variant (256 threads: 255 registers each)
+constexpr int kThreadsLoader = kThreads + kLoaderThreads;
 constexpr int kUBoxBytes = kTileP * kBoxK * 2;  // 16 KB: the 128 U rows of one 64-deep K box
 
 struct alignas(64) GemmParams {
@@ -62,6 +66,12 @@ struct alignas(64) GemmParams {
   uint32_t v_desc_hi, v_desc_lo;
   uint32_t u_kstep, v_kstep;  // start-address increment (16-byte units) per K=16 MMA inside a stage
   unsigned long long wait_limit_ns;  // time limit of every wait inside the kernel
+  // LOADER variants only: operands fetched by the loader warps instead of TMA (K-contiguous rows, 8-byte aligned)
+  const void* u_src;
+  const void* v_src;
+  long long u_pitch, v_pitch;  // bytes between consecutive rows
+  int u_cp, v_cp;              // 1: this operand comes through cp.async
+  uint32_t tma_tx_bytes;       // bytes per stage that TMA still delivers (both CTAs of a pair together)
 };
 
 // One piece of work of a CTA: K blocks kb0, kb0+kstep, ... (kbn of them) of output tile (tp, tq). When `partial`, the fp32 result goes to
@@ -181,7 +191,7 @@ struct SmemLayout {
   static constexpr int kBiasOff = kOutOff + kOutBytes;   // float[256]
   static constexpr int kBarOff = kBiasOff + 256 * 4;     // full[S], empty[S], acc_full[2], acc_empty[2]
   static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;  // tmem ptr, abort flag, last flag, epilogue verdict
-  static constexpr int kTotal = kMiscOff + 16;
+  static constexpr int kTotal = kMiscOff + 32;
   static constexpr int kDynBytes = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
 
@@ -278,14 +288,17 @@ __device__ __forceinline__ float load_in_as_float(const void* ptr, long long i, 
   return __half2float(reinterpret_cast<const __half*>(ptr)[i]);
 }
 
-template <int TILE_Q, int STAGES, int CG, int TK>
-__global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __grid_constant__ GemmParams p) {
+template <int TILE_Q, int STAGES, int CG, int TK, bool LOADER = false>
+__global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a16w16_sm100_kernel(const __grid_constant__ GemmParams p) {
   using L = SmemLayout<TILE_Q, STAGES, CG, TK>;
   constexpr int CW = TILE_Q >= 32 ? 32 : 16;  // columns per tcgen05.ld
   constexpr int NCHUNK = TILE_Q / CW;
   // TMEM is allocated in powers of two of at least 32 columns: two accumulators of TILE_Q columns each
   constexpr uint32_t kTmemCols = 2 * TILE_Q <= 32 ? 32 : 2 * TILE_Q <= 64 ? 64 : 2 * TILE_Q <= 128 ? 128 : 2 * TILE_Q <= 256 ? 256 : 512;
-  constexpr uint32_t kTxBytes = CG * L::kStageBytes;  // a pair's two CTAs both report to the leader's barrier
+  // a pair's two CTAs both report to the leader's barrier; with loader warps only the TMA-fetched operand counts
+  const uint32_t kTxBytes = LOADER ? p.tma_tx_bytes : (uint32_t)(CG * L::kStageBytes);
+  // arrivals that complete a stage: the producer's expect_tx, plus one per CTA from its loader warps
+  constexpr uint32_t kFullArrivals = LOADER ? 1 + CG : 1;
   constexpr int kVRows = L::kVRows;
   constexpr int kSlotVec = NCHUNK * (CW / 4) * kTileP;  // float4 per partial slot of one CTA
 
@@ -314,7 +327,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), kFullArrivals);
       mbar_init(empty_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -324,9 +337,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
     *abort_s = 0;
     *last_s = 0;
     *epi_abort_s = 0;
+    *(epi_abort_s + 1) = 0;  // the loader warps' verdict word
     fence_mbar_init();
-    prefetch_tmap(&p.tmap_u);
-    prefetch_tmap(&p.tmap_v);
+    if (!(LOADER && p.u_cp)) prefetch_tmap(&p.tmap_u);
+    if (!(LOADER && p.v_cp)) prefetch_tmap(&p.tmap_v);
     if (p.tma_store) prefetch_tmap(&p.tmap_out);
   }
   if (warp == 1) {
@@ -434,8 +448,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
           const uint32_t fb = full_target(stage);
           if (elect_one()) {
             if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), kTxBytes);
-            load_u(stage, kb, p0, fb);
-            load_v(stage, kb, q0, fb);
+            if (!(LOADER && p.u_cp)) load_u(stage, kb, p0, fb);
+            if (!(LOADER && p.v_cp)) load_v(stage, kb, q0, fb);
           }
           __syncwarp();
           ++issued;
@@ -577,7 +591,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
         __syncwarp();
       }
     }
-  } else {
+  } else if (!LOADER || warp < 6) {
     // ------------------------------------------------------------------ epilogue (warps 2..5 of every CTA)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     const int row = quarter * 32 + lane;
@@ -869,6 +883,101 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
       if (et == 0) trace_stamp(p, 2, it, 2);
     }
     if (lane == 0) tma_store_wait_all<0>();  // staging smem and C must be complete before the CTA leaves
+  } else if constexpr (LOADER) {
+    // ------------------------------------------------------------------ cp.async loaders (warps 6 and 7)
+    // Thread t copies the 16-byte piece t%8 of rows t/8, t/8 + 8, ... of every box: eight neighbouring threads read
+    // one 128-byte run of a row. Piece j of row r lands at position j ^ (r % 8) of the row's 128 bytes, which is
+    // where a SWIZZLE_128B tensor-map copy puts it (boxes start on 1024-byte boundaries). Rows past the operand's
+    // extent and K elements past K are zero-filled through the copy's source size, so nothing outside the logical
+    // matrix is ever read. A source that is only 8-byte aligned (odd rows of a pitch that is 8 mod 16) takes two
+    // 8-byte copies. The copies are plain (generic-proxy) writes: each thread waits for its own copies of a K
+    // block, fences them towards the async proxy that tcgen05.mma reads through, the two warps meet at a named
+    // barrier and one thread arrives on the stage's `full` barrier (the pair leader's, for both CTAs of a pair).
+    // A block is signalled kLag blocks after it was issued, so that several blocks of copies are in flight.
+    constexpr int kLag = STAGES - 1 < 3 ? STAGES - 1 : 3;
+    const int lt = threadIdx.x - kThreads;
+    const int lrow = lt >> 3, lj = lt & 7;
+    const uint32_t dst_off = (uint32_t)lrow * 128u + (uint32_t)((lj ^ (lrow & 7)) << 4);
+    volatile int* ld_abort_s = epi_abort_s + 1;  // shared word of the loader warps (zeroed below, before first use)
+    auto issue_box = [&](uint32_t box, const char* src0, long long pitch, int row0, int row_limit, int k0, int nrows) {
+      const int kk = k0 + lj * 8;  // first K element of this thread's piece
+      int kbytes = (p.K - kk) * 2;
+      kbytes = kbytes < 0 ? 0 : (kbytes > 16 ? 16 : kbytes);
+      for (int i = 0; i < nrows / 8; ++i) {
+        const int r = row0 + lrow + 8 * i;
+        const int nbytes = r < row_limit ? kbytes : 0;
+        const char* src = nbytes > 0 ? src0 + (long long)r * pitch + (long long)kk * 2 : src0;
+        const uint32_t dst = box + dst_off + (uint32_t)i * 1024u;
+        if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+          cp_async_16(dst, src, nbytes);
+        } else {
+          const int hi = nbytes - 8;
+          cp_async_8(dst, src, nbytes < 8 ? nbytes : 8);
+          cp_async_8(dst + 8u, hi > 0 ? src + 8 : src0, hi > 0 ? hi : 0);
+        }
+      }
+    };
+    int stage = 0, sig_stage = 0, pending = 0, issued = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    WorkIter wi;
+    wi.init(p, walker, walkers);
+    Unit w;
+    auto signal_oldest = [&]() {  // all loader threads call this together, after their own wait + fence
+      named_bar_sync(4, kLoaderThreads);
+      if (lt == 0) {
+        if constexpr (CG == 2)
+          mbar_arrive_cluster(full_bar(sig_stage), 0);
+        else
+          mbar_arrive(full_bar(sig_stage));
+      }
+      if (++sig_stage == STAGES) sig_stage = 0;
+      --pending;
+    };
+#pragma unroll 1
+    for (; ok && wi.next(p, w);) {
+      const int p0 = (w.tp * CG + rank) * kTileP, q0 = w.tq * TILE_Q + rank * kVRows;
+#pragma unroll 1
+      for (int kj = 0; kj < w.kbn; ++kj) {
+        const int kb = w.kb0 + kj * w.kstep;
+        if (issued >= STAGES) {
+          // One lane per warp polls (time limit only); the verdict is made common to the loader warps through shared
+          // memory and a named barrier, so that they leave together or not at all.
+          if (lane == 0 && !mbar_wait<CG == 2, false>(empty_bar(stage), phase ^ 1u, abort_s, wait_limit)) *ld_abort_s = 1;
+          named_bar_sync(5, kLoaderThreads);
+          if (*ld_abort_s != 0) {
+            if (lt == 0) report_abort(p, 4, w.tile);
+            ok = false;
+            break;
+          }
+        }
+        const uint32_t su = base + stage * L::kStageBytes;
+        const uint32_t sv = su + L::kUStageBytes;
+#pragma unroll
+        for (int sub = 0; sub < L::kSub; ++sub) {
+          const int k0 = kb * TK + sub * kBoxK;
+          if (p.u_cp) issue_box(su + sub * kUBoxBytes, reinterpret_cast<const char*>(p.u_src), p.u_pitch, p0, p.P, k0, kTileP);
+          if (p.v_cp) issue_box(sv + sub * L::kVBoxBytes, reinterpret_cast<const char*>(p.v_src), p.v_pitch, q0, p.Q, k0, kVRows);
+        }
+        cp_async_commit();
+        ++pending;
+        ++issued;
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        if (pending > kLag) {
+          cp_async_wait<kLag>();
+          fence_proxy_async_smem();
+          signal_oldest();
+        }
+      }
+    }
+    cp_async_wait<0>();  // every copy of this thread has landed (also when the loop was left early)
+    if (ok) {
+      fence_proxy_async_smem();
+      while (pending > 0) signal_oldest();
+    }
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -970,187 +1079,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_a16w16_sm100_kernel(const __
     tc_fence_after();
     tmem_dealloc<CG>(tmem_base, kTmemCols);
   }
-}
-
-// ---------------------------------------------------------------------------------------------------------
-// The bounded wait on its own: one thread waits on a barrier that nobody signals; the wait gives up after
-// `limit_ns` and the thread reports it in the 4-word status block like the GEMM roles do (role 9 = this test).
-__global__ void wait_selftest_kernel(int* status, unsigned long long limit_ns) {
-  __shared__ __align__(8) unsigned long long bar;
-  __shared__ int abort_flag;
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-    mbar_init(smem_u32(&bar), 1);
-    fence_mbar_init();
-    const bool completed = mbar_wait(smem_u32(&bar), 0u, &abort_flag, limit_ns);
-    if (!completed && atomicCAS(status, 0, 1) == 0) {
-      status[1] = (int)blockIdx.x;
-      status[2] = 9;
-      status[3] = -1;
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------------------------------------
-// Aligned repack: copies a 16-bit matrix whose base or pitch is not 16-byte aligned (TMA cannot describe it)
-// into a scratch image with a pitch that is a multiple of 8 elements. rows x cols, cols contiguous.
-// The reference rejects such operands (kernels/gemm_a16w16_gfx950.py:1322-1372); this path accepts them.
-__device__ __forceinline__ void repack_rows_body(const uint16_t* __restrict__ src, long long src_ld, uint16_t* __restrict__ dst,
-                                                 long long dst_ld, int rows, int cols, int block, int nblocks) {
-  const int chunks = (cols + 7) >> 3;
-  const long long total = (long long)rows * chunks;
-  for (long long i = block * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)nblocks * blockDim.x) {
-    const int r = (int)(i / chunks);
-    const int c0 = (int)(i - (long long)r * chunks) << 3;
-    const uint16_t* s = src + (long long)r * src_ld + c0;
-    uint32_t w[4] = {0, 0, 0, 0};
-    const int n = min(8, cols - c0);
-    if (n == 8 && (reinterpret_cast<uintptr_t>(s) & 7) == 0) {
-      const uint2 a = __ldg(reinterpret_cast<const uint2*>(s));
-      const uint2 b = __ldg(reinterpret_cast<const uint2*>(s) + 1);
-      w[0] = a.x, w[1] = a.y, w[2] = b.x, w[3] = b.y;
-    } else if (n == 8 && (reinterpret_cast<uintptr_t>(s) & 3) == 0) {
-      const uint32_t* s4 = reinterpret_cast<const uint32_t*>(s);
-      w[0] = __ldg(s4), w[1] = __ldg(s4 + 1), w[2] = __ldg(s4 + 2), w[3] = __ldg(s4 + 3);
-    } else {
-      for (int j = 0; j < n; ++j) w[j >> 1] |= uint32_t(__ldg(s + j)) << ((j & 1) * 16);
-    }
-    *reinterpret_cast<uint4*>(dst + (long long)r * dst_ld + c0) = make_uint4(w[0], w[1], w[2], w[3]);
-  }
-}
-
-// One launch repacks up to two operands: blocks [0, blocks0) take the first job, the rest the second.
-__global__ void repack_rows_kernel(const uint16_t* __restrict__ src0, long long src_ld0, uint16_t* __restrict__ dst0,
-                                   long long dst_ld0, int rows0, int cols0, int blocks0, const uint16_t* __restrict__ src1,
-                                   long long src_ld1, uint16_t* __restrict__ dst1, long long dst_ld1, int rows1, int cols1) {
-  if ((int)blockIdx.x < blocks0)
-    repack_rows_body(src0, src_ld0, dst0, dst_ld0, rows0, cols0, (int)blockIdx.x, blocks0);
-  else
-    repack_rows_body(src1, src_ld1, dst1, dst_ld1, rows1, cols1, (int)blockIdx.x - blocks0, (int)gridDim.x - blocks0);
-}
-
-// ---------------------------------------------------------------------------------------------------------
-// fp32 [rows, cols] (+ bias[cols] in `bias_dtype`) -> 16-bit or fp32 [rows, cols]; both row-major contiguous.
-// Final step of the K-sharded multi-GPU mode: the fp32 partial sums have been reduced across GPUs and are
-// rounded once here, exactly like the single-GPU epilogue.
-__global__ void cast_bias_rows_kernel(const float* __restrict__ in, void* __restrict__ out, const void* __restrict__ bias,
-                                      long long rows, int cols, int out_dtype, int bias_dtype) {
-  const long long total4 = rows * (long long)cols / 4;  // cols % 4 == 0 is checked by the host
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
-    float4 x = __ldcs(reinterpret_cast<const float4*>(in) + i);
-    if (bias != nullptr) {
-      const int c = (int)((i * 4) % cols);
-      x.x += load_in_as_float(bias, c, bias_dtype);
-      x.y += load_in_as_float(bias, c + 1, bias_dtype);
-      x.z += load_in_as_float(bias, c + 2, bias_dtype);
-      x.w += load_in_as_float(bias, c + 3, bias_dtype);
-    }
-    if (out_dtype == 1) {
-      reinterpret_cast<float4*>(out)[i] = x;
-    } else if (out_dtype == 2) {
-      __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
-      reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-    } else {
-      __half2 lo = __floats2half2_rn(x.x, x.y), hi = __floats2half2_rn(x.z, x.w);
-      reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------------------------------------
-// out[rows, cols] = cast(sum over s < n_slots of slots[s * slot_stride + ...] + bias[cols]); every slot is a
-// row-major contiguous fp32 [rows, cols] image. Owner-side reduction of the fused K-sharded multi-GPU mode: slot s
-// was filled over NVLink by rank s's GEMM epilogue (peer stores), slot `own` by this GPU's GEMM. The slots are
-// summed in index order, so every rank's result is bitwise independent of arrival order.
-__global__ void reduce_slots_kernel(const float* __restrict__ slots, long long slot_stride, int n_slots,
-                                    void* __restrict__ out, const void* __restrict__ bias, long long rows, int cols,
-                                    int out_dtype, int bias_dtype) {
-  const long long total4 = rows * (long long)cols / 4;  // cols % 4 == 0 is checked by the host
-  const long long stride4 = slot_stride / 4;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
-    const float4* src = reinterpret_cast<const float4*>(slots) + i;
-    float4 x = __ldcs(src);
-    int s = 1;
-    for (; s + 4 <= n_slots; s += 4) {  // four independent loads in flight per thread
-      const float4 a = __ldcs(src + s * stride4), b = __ldcs(src + (s + 1) * stride4);
-      const float4 c = __ldcs(src + (s + 2) * stride4), d = __ldcs(src + (s + 3) * stride4);
-      x.x = (((x.x + a.x) + b.x) + c.x) + d.x, x.y = (((x.y + a.y) + b.y) + c.y) + d.y;
-      x.z = (((x.z + a.z) + b.z) + c.z) + d.z, x.w = (((x.w + a.w) + b.w) + c.w) + d.w;
-    }
-    for (; s < n_slots; ++s) {
-      const float4 a = __ldcs(src + s * stride4);
-      x.x += a.x, x.y += a.y, x.z += a.z, x.w += a.w;
-    }
-    if (bias != nullptr) {
-      const int c = (int)((i * 4) % cols);
-      x.x += load_in_as_float(bias, c, bias_dtype);
-      x.y += load_in_as_float(bias, c + 1, bias_dtype);
-      x.z += load_in_as_float(bias, c + 2, bias_dtype);
-      x.w += load_in_as_float(bias, c + 3, bias_dtype);
-    }
-    if (out_dtype == 1) {
-      reinterpret_cast<float4*>(out)[i] = x;
-    } else if (out_dtype == 2) {
-      __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
-      reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-    } else {
-      __half2 lo = __floats2half2_rn(x.x, x.y), hi = __floats2half2_rn(x.z, x.w);
-      reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------------------------------------
-// Self-test helpers (b200_gemm_selftest): small-integer operands, an exact CUDA-core reference, an exact compare.
-__device__ __forceinline__ uint16_t selftest_encode_float(float v, int dtype) {
-  if (dtype == 2) {
-    __nv_bfloat16 h = __float2bfloat16_rn(v);
-    return *reinterpret_cast<uint16_t*>(&h);
-  }
-  __half h = __float2half_rn(v);
-  return *reinterpret_cast<uint16_t*>(&h);
-}
-__device__ __forceinline__ uint16_t selftest_encode(int v, int dtype) { return selftest_encode_float((float)v, dtype); }
-
-// dst[r * ld + c] = ((r * 131 + c * 71 + seed) % 5) - 2 for r < rows, c < cols, as bf16 / fp16.
-__global__ void selftest_fill_kernel(uint16_t* __restrict__ dst, int rows, int cols, long long ld, int dtype, int seed) {
-  const long long total = (long long)rows * cols;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
-    dst[(long long)r * ld + c] = selftest_encode(((r * 131 + c * 71 + seed) % 5) - 2, dtype);
-  }
-}
-
-// ref[m * N + n] = sum_k A[m,k] * B[k,n] + bias[n] in fp32 (exact for the small integers above).
-__global__ void selftest_ref_kernel(const uint16_t* __restrict__ a, long long lda, int a_trans, const uint16_t* __restrict__ b,
-                                    long long ldb, int b_trans, const uint16_t* __restrict__ bias, int M, int N, int K,
-                                    int dtype, float* __restrict__ ref) {
-  const long long total = (long long)M * N;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int m = (int)(i / N), n = (int)(i - (long long)m * N);
-    float acc = 0.f;
-    for (int k = 0; k < K; ++k) {
-      const float x = load_in_as_float(a, a_trans ? (long long)k * lda + m : (long long)m * lda + k, dtype);
-      const float y = load_in_as_float(b, b_trans ? (long long)n * ldb + k : (long long)k * ldb + n, dtype);
-      acc += x * y;
-    }
-    if (bias != nullptr) acc += load_in_as_float(bias, n, dtype);
-    ref[i] = acc;
-  }
-}
-
-// Counts elements of out (fp32, bf16 or fp16; row-major contiguous) that differ from the reference rounded the same way.
-__global__ void selftest_compare_kernel(const void* __restrict__ out, int out_dtype, const float* __restrict__ ref,
-                                        long long total, int* __restrict__ mismatches) {
-  int bad = 0;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    if (out_dtype == 1) {
-      bad += reinterpret_cast<const float*>(out)[i] != ref[i];
-    } else {
-      bad += reinterpret_cast<const uint16_t*>(out)[i] != selftest_encode_float(ref[i], out_dtype);
-    }
-  }
-  if (bad) atomicAdd(mismatches, bad);
 }
 
 }  // namespace b200

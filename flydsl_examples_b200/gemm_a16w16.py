@@ -220,6 +220,7 @@ def _fill_args(a, b, out, bias, pol: _policy.Policy, a_t: bool, b_t: bool) -> _l
     p.no_pdl = 0 if pol.pdl else 1
     p.tile_k = pol.tile_k
     p.wait_limit_us = pol.wait_limit_us
+    p.loader = 1 if pol.loader else 0
     return args
 
 

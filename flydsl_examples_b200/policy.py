@@ -47,7 +47,7 @@ REFERENCE_KEYS = (
 # Keys that only exist here.
 BLACKWELL_KEYS = ("tile_n", "swap_ab", "cta_group", "split_mode", "max_ctas", "stream_k", "tile_k")
 # Keys that switch behaviour without describing a tiling (they do not make a dict a "Blackwell policy").
-CONTROL_KEYS = ("strict_reference_envelope", "pdl", "wait_limit_us")
+CONTROL_KEYS = ("strict_reference_envelope", "pdl", "wait_limit_us", "loader")
 SPLIT_MODES = {"ticket": 0, "cluster": 2}
 
 
@@ -65,6 +65,9 @@ class Policy:
     pdl: bool = True         # programmatic dependent launch: set-up overlaps the previous kernel in the stream
     tile_k: int = 0          # K elements per pipeline stage; 0 = the tile's default (see tile_k())
     wait_limit_us: int = 0   # time limit of the kernel's waits in microseconds; 0 = 2 s
+    loader: bool = False     # True: K-contiguous operands TMA cannot describe (8- but not 16-byte aligned rows) are fetched
+                             # by loader warps inside the kernel (no scratch, one launch, much slower) instead of being
+                             # copied into an aligned image first
 
     def as_dict(self) -> dict:
         return asdict(self)
@@ -76,7 +79,7 @@ def smem_bytes(tile_n: int, stages: int, cta_group: int = 1, requested_tile_k: i
     staging = 4 * 2 * 32 * 128 if tile_n >= 64 else 0  # epilogue images for TMA stores
     staging = max(staging, TILE_M * tile_n * 4 if tile_n <= 64 else 0)  # rows received in cluster split-K mode
     tk = tile_k(tile_n, cta_group, requested_tile_k)
-    return stages * (TILE_M * tk * 2 + (tile_n // cta_group) * tk * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 16 + 1024
+    return stages * (TILE_M * tk * 2 + (tile_n // cta_group) * tk * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 32 + 1024
 
 
 def split_k_slices(k: int, split_k: int, tk: int = TILE_K) -> list[tuple[int, int]]:
@@ -282,13 +285,14 @@ def from_user_kwargs(user_kwargs: dict, m: int, n: int, k: int, layout: str, num
             fields["split_k"] = int(user_kwargs["split_k"])
         if "group_m" in user_kwargs:
             fields["group_m"] = int(user_kwargs["group_m"])
-    for key in ("pdl", "wait_limit_us"):
+    for key in ("pdl", "wait_limit_us", "loader"):
         if key in user_kwargs:
             fields[key] = user_kwargs[key]
     fields["swap_ab"] = bool(fields["swap_ab"])
     fields["stream_k"] = bool(fields["stream_k"])
     fields["pdl"] = bool(fields["pdl"])
     fields["wait_limit_us"] = int(fields["wait_limit_us"])
+    fields["loader"] = bool(fields["loader"])
     pol = Policy(**fields)
     return pol
 

@@ -65,7 +65,12 @@ typedef struct b200_gemm_policy {
                          to 128 wide); 0 = the tile's default (128 there, 64 for 256-wide tiles and CTA pairs)      */
   int32_t wait_limit_us; /* time limit of every wait inside the kernel, in microseconds; 0 = 2 seconds. A wait that
                             runs out makes the kernel give up, free what it holds and report through `status`       */
-  int32_t reserved[4];
+  int32_t loader; /* 1: fetch operands TMA cannot describe (base or pitch not a multiple of 16 bytes) inside the GEMM
+                     kernel with its cp.async loader warps instead of copying them into an aligned scratch image first:
+                     one launch and no scratch, for K-contiguous operands whose rows start on 8-byte boundaries. Two
+                     warps of 8- and 16-byte copies deliver a small fraction of what TMA does (config 4 'nt': 279 us
+                     against 43 us with the copy), so this is for callers without scratch, not for speed             */
+  int32_t reserved[3];
 } b200_gemm_policy;
 
 /* One GEMM call. Replaces the argument list of the reference's jit host stub gemm_a16w16_gfx950
@@ -111,6 +116,9 @@ typedef struct b200_gemm_plan {
   int32_t stream_k, sk_tiles, sk_slots; /* stream-K on; tiles cut into K spans; partial slots reserved per such tile */
   int32_t a_repacked, b_repacked; /* 1 when the operand is not TMA-encodable (base or pitch not 16-byte aligned)
                                      and is first copied into an aligned scratch image in the workspace        */
+  int32_t a_loader, b_loader;     /* 1 when such an operand is instead fetched inside the GEMM kernel by its loader
+                                     warps: K-contiguous rows that start on 8-byte boundaries (no copy, no scratch).
+                                     The ring depth is then the variant's deepest, whatever `stages` asked for  */
   uint64_t counter_bytes, partial_bytes, repack_bytes, workspace_bytes;
 } b200_gemm_plan;
 
@@ -127,7 +135,9 @@ int b200_gemm_a16w16(const b200_gemm_args* args, void* cuda_stream);
  *     partial tiles, repack images) comes from one array of B200_GEMM_STATIC_SCRATCH_BYTES built into the library; every
  *     GPU that loads the library holds that array until the process exits.
  *   - A call whose plan needs more scratch than that returns B200_GEMM_ERR_TOO_LARGE and launches nothing
- *     (b200_gemm_workspace_bytes tells the need beforehand). Calls that need no scratch are never limited.
+ *     (b200_gemm_workspace_bytes tells the need beforehand). Calls that need no scratch are never limited. When it is
+ *     the aligned copy of an operand TMA cannot describe that does not fit, the call switches policy.loader on by
+ *     itself, so that such operands are fetched inside the kernel where their layout allows.
  *   - It calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs stay the caller's.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
  *     current); make that first call outside any stream capture. Later calls reuse the address.

@@ -121,14 +121,19 @@ def test_config4_fp16_padded_offset_ktail(layout, kw):
     a_l, b_l, bias_l, ref = _c4_reference()
     a = O.place(a_l, layout[0] == "t", case.pad, case.offset, DEV)
     b = O.place(b_l, layout[1] == "t", case.pad, case.offset, DEV)
-    # K-contiguous operands have an 8328-byte pitch here: TMA cannot describe them, the repack path must run
-    pl = plan(a, b, layout, kw, out_dtype=torch.float32)
-    assert pl["a_repacked"] == (1 if layout[0] == "n" else 0)
-    assert pl["b_repacked"] == (1 if layout[1] == "t" else 0)
-    out = torch.full((case.m, case.n), float("nan"), dtype=torch.float32, device=DEV)
-    got = gemm_a16w16(a, b, out, bias=bias_l.to(DEV), user_kwargs=kw, layout=layout)
-    check_status()
-    O.assert_close(got, ref, case.k, f"c4 {layout} {kw}")
+    # K-contiguous operands have an 8328-byte pitch here: TMA cannot describe them, so they are copied into an
+    # aligned image first; their rows start on 8-byte boundaries, so on request the kernel's loader warps fetch them
+    # instead (one launch, no scratch). Both ways must give the oracle's result.
+    for loader in (False, True):
+        kw2 = {**kw, "loader": True} if loader else kw
+        pl = plan(a, b, layout, kw2, out_dtype=torch.float32)
+        assert pl["a_loader" if loader else "a_repacked"] == (1 if layout[0] == "n" else 0)
+        assert pl["b_loader" if loader else "b_repacked"] == (1 if layout[1] == "t" else 0)
+        assert pl["b_repacked" if loader else "b_loader"] == 0 and pl["a_repacked" if loader else "a_loader"] == 0
+        out = torch.full((case.m, case.n), float("nan"), dtype=torch.float32, device=DEV)
+        got = gemm_a16w16(a, b, out, bias=bias_l.to(DEV), user_kwargs=kw2, layout=layout)
+        check_status()
+        O.assert_close(got, ref, case.k, f"c4 {layout} {kw2}")
 
 
 def test_config5_large_bf16_sampled_and_consistent():
@@ -439,6 +444,62 @@ def test_unaligned_base_and_odd_pitch(layout):
     run_case(O.Case("unaligned", "bf16", layout, 150, 200, 333, seed=21, bias_std=0.5, pad=3, offset=1, user_kwargs={"tile_n": 64}))
     run_case(O.Case("unaligned_split", "fp16", layout, 150, 200, 1333, seed=22, out_dtype="fp32", pad=1, offset=7,
                     user_kwargs={"tile_n": 128, "split_k": 3}))
+
+
+LOADER_POLICIES = [
+    {"tile_n": 16, "swap_ab": True}, {"tile_n": 32, "tile_k": 64}, {"tile_n": 64}, {"tile_n": 64, "tile_k": 64, "split_k": 3},
+    {"tile_n": 128}, {"tile_n": 128, "tile_k": 64, "stream_k": True}, {"tile_n": 256}, {"tile_n": 128, "cta_group": 2},
+    {"tile_n": 192, "cta_group": 2}, {"tile_n": 256, "cta_group": 2}, {"tile_n": 256, "cta_group": 2, "stream_k": True},
+    {"tile_n": 32, "swap_ab": True, "split_k": 4, "split_mode": "cluster"},
+]
+
+
+@pytest.mark.parametrize("pad", [6, 14, 22])
+@pytest.mark.parametrize("idx", range(len(LOADER_POLICIES)))
+def test_loader_warps_fetch_8_byte_aligned_rows(pad, idx):
+    """Operands whose K-contiguous rows start on 8- but not 16-byte boundaries (pitch = K + pad = 1036, 1044 or 1052
+    elements, i.e. 8 mod 16 bytes) go through the cp.async loader warps of every tile family: ragged M, N and K (K = 1030 leaves a
+    6-element tail in the last 64-deep box, so pieces are cut at 4 and at 12 bytes), NaN-poisoned padding, both
+    dtypes, one or both operands on the loader, bit-equal to the aligned-copy path."""
+    kw = LOADER_POLICIES[idx]
+    small_n = kw["tile_n"] < 64 and not kw.get("swap_ab")
+    layouts = ("nt",) if (small_n or kw.get("swap_ab")) else ("nt", "tt") if kw["tile_n"] == 192 else ("nt", "nn", "tt")
+    for dtype, layout in [(d, l) for d in ("bf16", "fp16") for l in layouts]:
+        case = O.Case("loader", dtype, layout, 300, 456, 1030, seed=900 + idx + pad, bias_std=0.3, out_dtype="fp32" if idx % 2 else None,
+                      pad=pad, offset=4 * (idx % 3), user_kwargs=kw)
+        a, b, bias, a_l, b_l, bias_l = O.build_inputs(case, device=DEV)
+        pl = plan(a, b, layout, {**kw, "loader": True}, out_dtype=case.torch_out_dtype)
+        assert pl["a_loader"] == (1 if layout[0] == "n" else 0) and pl["b_loader"] == (1 if layout[1] == "t" else 0), pl
+        assert pl["a_repacked"] == 0 or layout[0] == "t"
+        ref = O.reference_matmul(a_l, b_l, bias_l, case.torch_out_dtype)
+        outs = []
+        for loader in (True, False):
+            out = torch.full((case.m, case.n), float("nan"), dtype=case.torch_out_dtype, device=DEV)
+            got = gemm_a16w16(a, b, out, bias=bias, user_kwargs={**kw, "loader": loader}, layout=layout)
+            check_status()
+            O.assert_close(got, ref, case.k, f"loader={loader} {dtype} {layout} pad {pad} {kw}")
+            outs.append(got.clone())
+        if not kw.get("stream_k") and kw.get("split_k", 1) == 1:
+            assert torch.equal(outs[0], outs[1])  # same tiles, same order of accumulation
+
+
+def test_loader_warps_exact_integers_full_tiles():
+    # small integers: fp32 accumulation is exact, so any misplaced 16-byte piece shows as a wrong integer
+    g = torch.Generator().manual_seed(5)
+    m, n, k = 512, 768, 2052
+    a_l = torch.randint(-2, 3, (m, k), generator=g).to(torch.bfloat16)
+    b_l = torch.randint(-2, 3, (k, n), generator=g).to(torch.bfloat16)
+    ref = (a_l.double() @ b_l.double()).float()
+    for layout in ("nt", "nn", "tt"):
+        a = O.place(a_l, layout[0] == "t", 8, 8, DEV)   # K pitch 2060 elements = 4120 bytes: 8 mod 16
+        b = O.place(b_l, layout[1] == "t", 8, 8, DEV)
+        for kw in ({"tile_n": 256, "cta_group": 2}, {"tile_n": 128}, {"tile_n": 192, "cta_group": 2} if layout[1] == "t" else {"tile_n": 64}):
+            kw = {**kw, "loader": True}
+            pl = plan(a, b, layout, kw, out_dtype=torch.float32)
+            assert pl["a_loader"] + pl["b_loader"] >= 1
+            got = gemm_a16w16(a, b, layout=layout, out_dtype=torch.float32, user_kwargs=kw)
+            check_status()
+            assert torch.equal(got.cpu(), ref), (layout, kw)
 
 
 def test_allocates_output_with_default_policy():

@@ -182,11 +182,25 @@ def test_plan_flags_operands_tma_cannot_describe():
     a = torch.as_strided(buf, (1000, 4100), (4164, 1), 128)
     bbuf = torch.empty(4100 * 3064 + 256, dtype=torch.float16)
     b = torch.as_strided(bbuf, (4100, 3000), (3064, 1), 128)
+    # TMA cannot describe it: by default it is copied into an aligned image first
     pl = plan(a, b, "nn", {"tile_n": 128}, out_dtype=torch.float32)
-    assert pl["a_repacked"] == 1
+    assert (pl["a_loader"], pl["a_repacked"]) == (0, 1)
     assert pl["repack_bytes"] >= 1000 * 4104 * 2
     if b.data_ptr() % 16 == 0:
-        assert pl["b_repacked"] == 0
+        assert (pl["b_loader"], pl["b_repacked"]) == (0, 0)
+    # its rows start on 8-byte boundaries, so on request the loader warps of the kernel fetch it: no copy, no scratch
+    pl = plan(a, b, "nn", {"tile_n": 128, "loader": True}, out_dtype=torch.float32)
+    assert (pl["a_loader"], pl["a_repacked"], pl["repack_bytes"]) == (1, 0, 0)
+    assert pl["stages"] == 3  # the one ring depth the loader variant of this tile is built with
+    # rows that start on odd 4-byte boundaries (pitch 4102 elements) are beyond the loader: copied
+    buf2 = torch.empty(1000 * 4102 + 256, dtype=torch.float16)
+    a2 = torch.as_strided(buf2, (1000, 4100), (4102, 1), 128)
+    pl = plan(a2, b, "nn", {"tile_n": 128, "loader": True}, out_dtype=torch.float32)
+    assert (pl["a_loader"], pl["a_repacked"]) == (0, 1)
+    # an M-contiguous operand TMA cannot take (pitch 1001 elements) is copied too
+    a3 = torch.as_strided(torch.empty(4100 * 1001 + 256, dtype=torch.float16), (1000, 4100), (1, 1001), 128)
+    pl = plan(a3, b, "tn", {"tile_n": 128, "loader": True}, out_dtype=torch.float32)
+    assert (pl["a_loader"], pl["a_repacked"]) == (0, 1)
 
 
 def test_tuned_table_roundtrip(tmp_path):

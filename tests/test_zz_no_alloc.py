@@ -71,6 +71,24 @@ def test_static_scratch_refuses_plans_beyond_its_limit():
     assert bool((out == 7.0).all()), "nothing may have been launched"
 
 
+def test_static_scratch_falls_back_to_the_loader_warps_for_large_unaligned_operands():
+    # config 4 'nt': aligned copies of both operands would take 32.8 MB, twice the built-in array; the entry point then
+    # has the kernel's loader warps fetch them, and the call needs no scratch at all
+    lib = _lib.load()
+    case = O.CONFIGS["c4_nt"]
+    a, b, bias, a_l, b_l, bias_l = O.build_inputs(case, device=DEV)
+    out = torch.full((case.m, case.n), float("nan"), dtype=torch.float32, device=DEV)
+    args = _args_for(case, a, b, out, bias)
+    assert lib.b200_gemm_workspace_bytes(C.byref(args)) > _lib.STATIC_SCRATCH_BYTES
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    args.status = status.data_ptr()
+    rc = lib.b200_gemm_a16w16_static_scratch(C.byref(args), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, _lib.strerror(rc)
+    torch.cuda.synchronize()
+    assert status.tolist()[0] == 0
+    O.assert_close(out, O.reference_matmul(a_l, b_l, bias_l, torch.float32), case.k, "c4_nt through the built-in scratch entry")
+
+
 def test_static_scratch_needs_no_scratch_for_plain_tiles():
     lib = _lib.load()
     case = O.Case("plain", "bf16", "nt", 256, 512, 1024, seed=65, user_kwargs={"tile_n": 128})
