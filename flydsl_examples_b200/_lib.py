@@ -91,6 +91,8 @@ class Plan(C.Structure):
         ("partial_bytes", C.c_uint64),
         ("repack_bytes", C.c_uint64),
         ("workspace_bytes", C.c_uint64),
+        ("atomic_out", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
     def as_dict(self) -> dict:

@@ -67,6 +67,26 @@ __global__ void repack_rows_kernel(const uint16_t* __restrict__ src0, long long 
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// out[r, c] = bias[c] (or 0) for an fp32 matrix with row stride ldo: what C must hold before a GEMM whose K-parallel
+// units add their partial sums into it (atomic split mode). cols % 4 == 0 and 16-byte aligned rows (the same
+// condition that lets the GEMM reach C through TMA).
+__global__ void init_out_rows_kernel(float* __restrict__ out, long long ldo, int rows, int cols, const void* __restrict__ bias,
+                                     int bias_dtype) {
+  grid_launch_dependents();  // the GEMM behind may set up meanwhile; it touches C only after this grid has completed
+  const int c4 = cols >> 2;
+  const long long total = (long long)rows * c4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / c4), c = (int)(i - (long long)r * c4) << 2;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (bias != nullptr) {
+      x.x = load_in_as_float(bias, c, bias_dtype), x.y = load_in_as_float(bias, c + 1, bias_dtype);
+      x.z = load_in_as_float(bias, c + 2, bias_dtype), x.w = load_in_as_float(bias, c + 3, bias_dtype);
+    }
+    *reinterpret_cast<float4*>(out + (long long)r * ldo + c) = x;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // fp32 [rows, cols] (+ bias[cols] in `bias_dtype`) -> 16-bit or fp32 [rows, cols]; both row-major contiguous.
 // Final step of the K-sharded multi-GPU mode: the fp32 partial sums have been reduced across GPUs and are
 // rounded once here, exactly like the single-GPU epilogue.

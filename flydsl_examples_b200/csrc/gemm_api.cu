@@ -254,12 +254,22 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
         pl.stages * (kTileP * pl.tile_k * 2 + pl.tile_n * pl.tile_k * 2) < kTileP * pl.tile_n * 4)
       return B200_GEMM_ERR_BAD_POLICY;
   }
-  const bool tickets = (pl.split_k > 1 && pl.cluster_split == 0) || pl.sk_tiles > 0;
+  // Atomic mode: K-parallel units add their fp32 sums straight into C with TMA reduce-add. Needs an fp32 C that TMA can
+  // reach (16-byte aligned rows, a whole number of 4-column groups), tiles at least 64 wide and C written untransposed;
+  // where that does not hold the ticket mode is used instead (plan.atomic_out tells which).
+  const bool k_parallel = (pl.split_k > 1 && pl.cluster_split == 0) || pl.sk_tiles > 0;
+  pl.atomic_out = (pol.split_mode == B200_GEMM_SPLIT_ATOMIC && k_parallel && a->out_dtype == B200_GEMM_DTYPE_FP32 &&
+                   !pl.swap_ab && pl.tile_n >= 64 && (reinterpret_cast<uintptr_t>(a->out) & 15) == 0 && (a->ldo & 3) == 0 &&
+                   (a->n & 3) == 0)
+                      ? 1
+                      : 0;
+  const bool tickets = k_parallel && !pl.atomic_out;
   if (tickets && tiles * pl.cta_group > (int64_t)(kCounterBytes / 4)) return B200_GEMM_ERR_TOO_LARGE;
   // The ticket region has a fixed size and is reserved by every call that uses the workspace at all, so that no call
   // ever writes partial sums or a repack image where another call keeps its tickets.
   pl.counter_bytes = (tickets || pl.a_repacked || pl.b_repacked) ? kCounterBytes : 0;
-  pl.partial_bytes = pl.sk_tiles > 0 ? (uint64_t)pl.sk_tiles * pl.sk_slots * pl.tile_m * pl.tile_n * 4
+  pl.partial_bytes = pl.atomic_out   ? 0
+                     : pl.sk_tiles > 0 ? (uint64_t)pl.sk_tiles * pl.sk_slots * pl.tile_m * pl.tile_n * 4
                      : (pl.split_k > 1 && pl.cluster_split == 0) ? (uint64_t)pl.num_units * pl.tile_m * pl.tile_n * 4
                                                                  : 0;
   const uint64_t ra = pl.a_repacked ? round_up((uint64_t)a_rows * r->ra_ld * 2, 256) : 0;
@@ -336,6 +346,8 @@ struct b200_gemm_handle {
   int grid, threads, smem_bytes, device, cta_group, cluster_split, pdl;
   int n_repack;
   b200::RepackJob repack[2];
+  int init_out;  // atomic split mode: C is set to the bias (or zero) by a small kernel before the GEMM
+  int m, n, bias_dtype;
   b200_gemm_plan plan;
 };
 
@@ -422,6 +434,10 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
         p.tma_store = 1;
     }
   }
+  p.atomic_out = pl.atomic_out;
+  if (pl.atomic_out && !p.tma_store) return B200_GEMM_ERR_TENSOR_MAP;
+  h->init_out = pl.atomic_out;
+  h->m = (int)a->m, h->n = (int)a->n, h->bias_dtype = a->in_dtype;
   p.tickets = reinterpret_cast<int*>(ws);
   p.partials = reinterpret_cast<float*>(ws + r.off_partials);
   p.status = a->status;
@@ -483,6 +499,15 @@ static int run(const b200_gemm_handle* h, cudaStream_t stream) {
                                                                   j1.src, j1.src_ld, j1.dst, j1.dst_ld, j1.rows, j1.cols);
     cudaError_t re = cudaGetLastError();
     if (re != cudaSuccess) return set_cuda_error(re);
+  }
+  if (h->init_out) {
+    const long long total4 = (long long)h->m * (h->n / 4);
+    const long long want = (total4 + 255) / 256;
+    const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+    init_out_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<float*>(h->params.out), h->params.ldo, h->m, h->n,
+                                                     h->params.bias, h->bias_dtype);
+    cudaError_t ie = cudaGetLastError();
+    if (ie != cudaSuccess) return set_cuda_error(ie);
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));

@@ -57,6 +57,8 @@ struct alignas(64) GemmParams {
   int group_p;      // grouped rasterisation over tile rows of P (0 = off)
   int swap_out;     // 1: D^T is written (out[q*ldo + p]); bias indexed by p
   int tma_store;    // 1: finished tiles leave through swizzled staging smem and TMA stores (needs 16-byte aligned C rows)
+  int atomic_out;   // 1: a partial unit adds its fp32 sums straight into `out` with TMA reduce-add (no workspace, no tickets);
+                    //    `out` (fp32) holds the bias, or zero, before the kernel starts, and whole tiles overwrite it
   int out_dtype;    // 1 fp32, 2 bf16, 3 fp16
   int in_dtype;     // 2 bf16, 3 fp16
   int u_mn_major;   // 1: U is P-contiguous, loaded as two [64 P x 64 K] boxes
@@ -677,7 +679,9 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
       }
       // TMA-store path: bias + cast, then this lane's row segment goes into the warp's swizzled staging image
       // (16-byte chunk j of row t sits at position j ^ (t % 8)); every full 128-byte row image is stored by one lane.
-      const bool staged = direct && p.tma_store != 0 && TILE_Q >= 64;
+      // K-parallel units of the atomic mode leave like whole tiles, except that their boxes are added to C
+      const bool red = !direct && p.atomic_out != 0;
+      const bool staged = (direct || red) && p.tma_store != 0 && TILE_Q >= 64;
       // The warp normally alternates between two 4 KB staging images and waits for the TMA store that last read one
       // before rewriting it. In a CTA's last work item nothing will be loaded into the operand ring any more and the
       // accumulator being complete means the ring has been read: every flush then gets an image of its own in the ring
@@ -696,8 +700,12 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
         const int row0 = (w.tp * CG + rank) * kTileP + quarter * 32;
         if (lane == 0) {
           // a box that starts outside C holds nothing to write; one that straddles the edge is clipped by TMA
-          if (row0 < p.P && col0 < p.Q)
-            tma_store_2d(&p.tmap_out, col0, row0, stage_image());
+          if (row0 < p.P && col0 < p.Q) {
+            if (red)
+              tma_reduce_add_2d(&p.tmap_out, col0, row0, stage_image());
+            else
+              tma_store_2d(&p.tmap_out, col0, row0, stage_image());
+          }
           tma_store_commit();
         }
         ++out_flip;
@@ -714,7 +722,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
         for (int i = 0; i < CW; ++i) v[i] = __uint_as_float(r[i]);
         if (staged) {
           if constexpr (CW == 32) {
-            if (p.bias != nullptr) {
+            if (p.bias != nullptr && !red) {  // in the atomic mode C already holds the bias
               const float4* b4 = reinterpret_cast<const float4*>(bias_s + c * CW);  // 16-byte aligned: one load per 4 columns
 #pragma unroll
               for (int j = 0; j < CW / 4; ++j) {
@@ -827,7 +835,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
       }
 
       if (et == 0) trace_stamp(p, 2, it, 1);
-      if (!direct && !cluster_mode) {
+      if (!direct && !cluster_mode && !red) {
         // Ticket: the CTA that arrives last at this (half-)tile sums all contributions in slot order.
         // One thread fences for the group: the barrier orders every epilogue thread's partial stores before its
         // fence (release, cumulative), and its second fence (acquire) plus the barrier orders the reads after.

@@ -137,6 +137,13 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, int x, int y, uin
                "r"(x), "r"(y), "r"(src)
                : "memory");
 }
+// Same box, added element by element to what global memory holds (the addition happens in L2; fp32 here).
+__device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, int x, int y, uint32_t src) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(x), "r"(y), "r"(src)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {

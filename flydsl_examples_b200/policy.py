@@ -48,7 +48,7 @@ REFERENCE_KEYS = (
 BLACKWELL_KEYS = ("tile_n", "swap_ab", "cta_group", "split_mode", "max_ctas", "stream_k", "tile_k")
 # Keys that switch behaviour without describing a tiling (they do not make a dict a "Blackwell policy").
 CONTROL_KEYS = ("strict_reference_envelope", "pdl", "wait_limit_us", "loader")
-SPLIT_MODES = {"ticket": 0, "cluster": 2}
+SPLIT_MODES = {"ticket": 0, "atomic": 1, "cluster": 2}
 
 
 @dataclass(frozen=True)

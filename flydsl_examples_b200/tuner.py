@@ -71,6 +71,9 @@ def candidate_configs(args: TuneArgs, num_sms: int = P.NUM_SMS_DEFAULT) -> list[
                 for s in (2, 4, 8, 16):  # K slices as one thread-block cluster
                     if s <= kb and tiles * s <= 2 * walkers:
                         splits.append((s, False, "cluster"))
+        if args.out_dtype == "fp32" and not swap and tile_n >= 64:
+            # fp32 outputs: K-parallel units may add their tiles straight into C (no workspace, no second pass)
+            splits += [(s, sk, "atomic") for (s, sk, mode) in list(splits) if mode == "ticket" and (s > 1 or sk)]
         groups = (0, 4, 8) if tiles >= 2 * walkers else (0,)
         for stages, (split_k, stream_k, mode), group_m in itertools.product(stage_opts, splits, groups):
             cfg = {"tile_n": tile_n, "cta_group": cg, "stages": stages, "split_k": split_k, "stream_k": stream_k,

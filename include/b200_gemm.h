@@ -38,7 +38,14 @@ extern "C" {
 /* split-K reduction modes */
 #define B200_GEMM_SPLIT_TICKET 0 /* fp32 partial tiles in the workspace; the last-arriving CTA of a tile sums them in
                                     slice order, adds bias and casts once (deterministic; never waits)            */
-#define B200_GEMM_SPLIT_ATOMIC 1  /* reserved                                                                      */
+#define B200_GEMM_SPLIT_ATOMIC 1  /* fp32 outputs: every K slice (or stream-K span) adds its fp32 tile straight into C
+                                     with TMA reduce-add (the additions happen in L2), after a small kernel has set C to
+                                     the bias (or zero): no workspace, no tickets, no second pass; the order of the
+                                     additions, and so the last bits of the result, vary from run to run. Needs an
+                                     fp32 C with 16-byte aligned rows, tile_n >= 64, no swap_ab; otherwise the ticket mode
+                                     runs (b200_gemm_plan.atomic_out tells). Takes the place of the reference's atomic
+                                     split-K epilogue (kernels/gemm_a16w16_gfx950.py:325-375), in fp32 instead of
+                                     packed 16-bit                                                                  */
 #define B200_GEMM_SPLIT_CLUSTER 2 /* the K slices of a tile are the CTAs of one thread-block cluster (2, 4, 8 or 16);
                                      each CTA sends its partial rows to the row's owner through distributed shared
                                      memory, a cluster barrier, owners sum in rank order. No workspace, no tickets,
@@ -120,6 +127,8 @@ typedef struct b200_gemm_plan {
                                      warps: K-contiguous rows that start on 8-byte boundaries (no copy, no scratch).
                                      The ring depth is then the variant's deepest, whatever `stages` asked for  */
   uint64_t counter_bytes, partial_bytes, repack_bytes, workspace_bytes;
+  int32_t atomic_out;  /* 1: the atomic split mode is in effect (one more small launch sets C to the bias beforehand) */
+  int32_t reserved;
 } b200_gemm_plan;
 
 /* Launch the GEMM on `cuda_stream` (a cudaStream_t; NULL = legacy default stream) of the current device.

@@ -502,6 +502,57 @@ def test_loader_warps_exact_integers_full_tiles():
             assert torch.equal(got.cpu(), ref), (layout, kw)
 
 
+ATOMIC_POLICIES = [
+    {"tile_n": 64, "split_k": 3}, {"tile_n": 128, "split_k": 2}, {"tile_n": 128, "tile_k": 64, "stream_k": True},
+    {"tile_n": 256, "split_k": 4}, {"tile_n": 256, "stream_k": True}, {"tile_n": 128, "cta_group": 2, "split_k": 2},
+    {"tile_n": 256, "cta_group": 2, "stream_k": True}, {"tile_n": 256, "cta_group": 2, "split_k": 3},
+    {"tile_n": 192, "cta_group": 2, "stream_k": True},
+]
+
+
+@pytest.mark.parametrize("idx", range(len(ATOMIC_POLICIES)))
+def test_atomic_split_mode_adds_partial_tiles_into_fp32_output(idx):
+    """split_mode 'atomic': K slices / stream-K spans add their fp32 tiles into C with TMA reduce-add after a small
+    kernel has put the bias (or zero) there. No workspace; the result is within the split-K bound of the contract
+    (the order of the additions is not fixed). Ragged M, N, K; outputs pre-filled with NaN; repeated calls."""
+    kw = {**ATOMIC_POLICIES[idx], "split_mode": "atomic"}
+    layouts = ("nt", "tt") if kw["tile_n"] == 192 else LAYOUTS
+    for dtype, layout, bias in [("bf16", layouts[0], 0.5), ("fp16", layouts[-1], None), ("bf16", layouts[1], 0.5)]:
+        case = O.Case("atomic", dtype, layout, 700, 936, 2100, seed=300 + idx, bias_std=bias, out_dtype="fp32", user_kwargs=kw)
+        a, b, bias_d, a_l, b_l, bias_l = O.build_inputs(case, device=DEV)
+        pl = plan(a, b, layout, kw, out_dtype=torch.float32, bias=bias_d)
+        assert pl["atomic_out"] == 1 and pl["partial_bytes"] == 0, pl  # no partial tiles in the workspace
+        run_case(case, repeats=3)
+
+
+def test_atomic_split_mode_falls_back_where_it_cannot_apply():
+    # 16-bit output, or C written transposed (swap_ab), or a C row pitch TMA cannot take: the ticket mode runs
+    a = torch.empty(300, 2048, dtype=torch.bfloat16)
+    b = torch.empty(520, 2048, dtype=torch.bfloat16).t()
+    kw = {"tile_n": 128, "split_k": 4, "split_mode": "atomic"}
+    assert plan(a, b, "nt", kw, out_dtype=torch.float32)["atomic_out"] == 1
+    pl = plan(a, b, "nt", kw, out_dtype=torch.bfloat16)
+    assert pl["atomic_out"] == 0 and pl["partial_bytes"] > 0
+    assert plan(a, b, "nt", {**kw, "tile_n": 64, "swap_ab": True}, out_dtype=torch.float32)["atomic_out"] == 0
+    assert plan(a, b[:, :518], "nt", kw, out_dtype=torch.float32)["atomic_out"] == 0  # N = 518: rows of C not 16-byte aligned
+    run_case(O.Case("atomic_bf16", "bf16", "nt", 300, 520, 2048, seed=41, bias_std=0.5, user_kwargs=kw))
+    run_case(O.Case("atomic_odd_n", "bf16", "nt", 300, 518, 2048, seed=42, bias_std=0.5, out_dtype="fp32", user_kwargs=kw))
+
+
+def test_config4_atomic_stream_k():
+    a_l, b_l, bias_l, ref = _c4_reference()
+    for layout in LAYOUTS:
+        case = O.CONFIGS[f"c4_{layout}"]
+        a = O.place(a_l, layout[0] == "t", case.pad, case.offset, DEV)
+        b = O.place(b_l, layout[1] == "t", case.pad, case.offset, DEV)
+        kw = {"tile_n": 256, "cta_group": 2, "stream_k": True, "split_mode": "atomic"}
+        for rep in range(2):
+            out = torch.full((case.m, case.n), float("nan"), dtype=torch.float32, device=DEV)
+            got = gemm_a16w16(a, b, out, bias=bias_l.to(DEV), user_kwargs=kw, layout=layout)
+            check_status()
+            O.assert_close(got, ref, case.k, f"c4 {layout} atomic stream-K call {rep}")
+
+
 def test_allocates_output_with_default_policy():
     a_l = torch.randn(64, 256).to(torch.bfloat16)
     b_l = torch.randn(256, 64).to(torch.bfloat16)
