@@ -54,3 +54,51 @@ def test_operator_inside_torch_compile():
     y = f(a, b)
     check_status()
     O.assert_close(y, O.reference_matmul(a_l, b_l, None, torch.float32) * 2.0, case.k, "compiled")
+
+
+@pytest.mark.gpu
+def test_operator_inside_torch_compile_inductor():
+    # the default compiler back end: the operator stays an opaque call, the multiply around it is compiled
+    from flydsl_examples_b200.gemm_a16w16 import check_status
+    from oracle import oracle as O
+
+    case = O.Case("op_inductor", "bf16", "nt", 96, 256, 512, seed=73, bias_std=0.5)
+    a, b, bias, a_l, b_l, bias_l = O.build_inputs(case, device="cuda")
+
+    def f(x, w, bb):
+        return torch.ops.b200.gemm_a16w16(x, w, bb, "nt", "fp32") * 2.0 + 1.0
+
+    try:
+        compiled = torch.compile(f, fullgraph=True)
+        y = compiled(a, b, bias)
+    except Exception as exc:  # no host compiler / code generator on this machine
+        if "b200" in str(exc) or "gemm_a16w16" in str(exc):
+            raise
+        pytest.skip(f"the inductor back end cannot build here: {type(exc).__name__}")
+    check_status()
+    O.assert_close(y, O.reference_matmul(a_l, b_l, bias_l, torch.float32) * 2.0 + 1.0, case.k, "inductor")
+
+
+@pytest.mark.gpu
+def test_operator_under_cuda_graph_capture():
+    # a decode loop captures the call once and replays it; new inputs are copied into the captured buffers
+    from flydsl_examples_b200.gemm_a16w16 import check_status
+    from oracle import oracle as O
+
+    case = O.Case("op_graph", "bf16", "nt", 32, 384, 1024, seed=74, user_kwargs={})
+    a, b, _, a_l, b_l, _ = O.build_inputs(case, device="cuda")
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        torch.ops.b200.gemm_a16w16(a, b, None, "nt", "fp32")  # warm-up: workspace and launch handle exist before capture
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            y = torch.ops.b200.gemm_a16w16(a, b, None, "nt", "fp32")
+    torch.cuda.synchronize()
+    for step in range(3):
+        a_new = (torch.randn(case.m, case.k, generator=torch.Generator().manual_seed(step)) * 0.5).to(torch.bfloat16)
+        a.copy_(a_new.to("cuda"))
+        graph.replay()
+        torch.cuda.synchronize()
+        check_status()
+        O.assert_close(y, O.reference_matmul(a_new, b_l, None, torch.float32), case.k, f"graph replay {step}")
