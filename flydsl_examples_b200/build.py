@@ -81,7 +81,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if verbose:
         for _, log in results:
             sys.stderr.write(log)
-    cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *[str(obj) for obj, _ in results]]
+    cmd = [_nvcc(), "-shared", "-Wno-deprecated-gpu-targets", "-o", str(LIB_PATH), *[str(obj) for obj, _ in results]]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("link failed:\n" + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
