@@ -73,9 +73,21 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     compiled side by side (one nvcc process each), then linked into one shared object."""
     if not force and is_current():
         return LIB_PATH
-    from concurrent.futures import ThreadPoolExecutor
+    import fcntl
 
     OBJ_DIR.mkdir(exist_ok=True)
+    # One builder at a time: the ranks of a multi-GPU job import this package at the same moment, and the first one
+    # that finds the library stale builds it while the others wait here and then find it current.
+    with open(OBJ_DIR / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and is_current():
+            return LIB_PATH
+        return _build_locked(verbose)
+
+
+def _build_locked(verbose: bool) -> Path:
+    from concurrent.futures import ThreadPoolExecutor
+
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
         results = list(pool.map(lambda src: _compile_one(src, verbose), SOURCES))
     if verbose:

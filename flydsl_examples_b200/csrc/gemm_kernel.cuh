@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
   // TMEM is allocated in powers of two of at least 32 columns: two accumulators of TILE_Q columns each
   constexpr uint32_t kTmemCols = 2 * TILE_Q <= 32 ? 32 : 2 * TILE_Q <= 64 ? 64 : 2 * TILE_Q <= 128 ? 128 : 2 * TILE_Q <= 256 ? 256 : 512;
   // a pair's two CTAs both report to the leader's barrier; with loader warps only the TMA-fetched operand counts
-  const uint32_t kTxBytes = LOADER ? p.tma_tx_bytes : (uint32_t)(CG * L::kStageBytes);
+  const uint32_t tx_bytes = LOADER ? p.tma_tx_bytes : (uint32_t)(CG * L::kStageBytes);
   // arrivals that complete a stage: the producer's expect_tx, plus one per CTA from its loader warps
   constexpr uint32_t kFullArrivals = LOADER ? 1 + CG : 1;
   constexpr int kVRows = L::kVRows;
@@ -449,7 +449,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
           if (kj == 0 && lane == 0) trace_stamp(p, 0, item, 1);
           const uint32_t fb = full_target(stage);
           if (elect_one()) {
-            if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), kTxBytes);
+            if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), tx_bytes);
             if (!(LOADER && p.u_cp)) load_u(stage, kb, p0, fb);
             if (!(LOADER && p.v_cp)) load_v(stage, kb, q0, fb);
           }
@@ -906,7 +906,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
     const int lt = threadIdx.x - kThreads;
     const int lrow = lt >> 3, lj = lt & 7;
     const uint32_t dst_off = (uint32_t)lrow * 128u + (uint32_t)((lj ^ (lrow & 7)) << 4);
-    volatile int* ld_abort_s = epi_abort_s + 1;  // shared word of the loader warps (zeroed below, before first use)
+    volatile int* ld_abort_s = epi_abort_s + 1;  // shared word of the loader warps (zeroed with the other flags at kernel start)
     auto issue_box = [&](uint32_t box, const char* src0, long long pitch, int row0, int row_limit, int k0, int nrows) {
       const int kk = k0 + lj * 8;  // first K element of this thread's piece
       int kbytes = (p.K - kk) * 2;
