@@ -92,3 +92,30 @@ def test_wait_selftest_validates_its_arguments():
     assert lib.b200_gemm_wait_selftest(None, 100, None) == -1
     assert lib.b200_gemm_wait_selftest(C.c_void_p(4096), 0, None) == -1         # no limit given
     assert lib.b200_gemm_wait_selftest(C.c_void_p(4096), 2_000_000, None) == -1  # beyond one second
+
+
+def test_ctypes_structures_match_the_header(tmp_path):
+    """The Python binding restates the header's structs by hand: compile the header with the host C compiler and compare
+    sizes and the offsets of the last members, so that a field added on one side only is caught here and not on a GPU."""
+    import shutil
+    import subprocess
+
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        import pytest
+
+        pytest.skip("no host C compiler")
+    src = tmp_path / "layout.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <stddef.h>\n#include "b200_gemm.h"\n'
+        "int main(void) {\n"
+        '  printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(b200_gemm_policy), sizeof(b200_gemm_args), sizeof(b200_gemm_plan),\n'
+        "         sizeof(b200_peer_handle), offsetof(b200_gemm_policy, reserved), offsetof(b200_gemm_args, trace_words),\n"
+        "         offsetof(b200_gemm_plan, atomic_out), offsetof(b200_gemm_args, policy));\n"
+        "  return 0;\n}\n")
+    exe = tmp_path / "layout"
+    subprocess.run([cc, "-std=c99", f"-I{ROOT / 'include'}", "-o", str(exe), str(src)], check=True)
+    got = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    want = [C.sizeof(_lib.Policy), C.sizeof(_lib.Args), C.sizeof(_lib.Plan), C.sizeof(_lib.PeerHandle),
+            _lib.Policy.reserved.offset, _lib.Args.trace_words.offset, _lib.Plan.atomic_out.offset, _lib.Args.policy.offset]
+    assert got == want, (got, want)
