@@ -1005,7 +1005,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
     cluster_wait();
   }
   if constexpr (CG == 1) {
-    if (cluster_mode && warp >= 2) {
+    if (cluster_mode && warp >= 2 && warp < 6) {  // the epilogue warps (a LOADER variant has two more warps behind them)
       // Each CTA owns R = 128/S rows of the tile: sum the S slabs in rank order (deterministic), bias, cast, store.
       const int S = p.cluster_split, R = kTileP / S;
       const int crank = (int)cluster_ctarank();
