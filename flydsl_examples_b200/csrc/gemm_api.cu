@@ -61,6 +61,7 @@ struct Variant {
 static const Variant kVariants[] = {
     {16, 1, 128, 5}, {32, 1, 128, 5}, {64, 1, 128, 4}, {128, 1, 128, 3}, {256, 1, 64, 4}, {128, 2, 64, 8},
     {256, 2, 64, 6}, {192, 2, 64, 6}, {16, 1, 64, 8},  {32, 1, 64, 8},   {64, 1, 64, 8},  {128, 1, 64, 6},
+    {512, 2, 64, 4},
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 constexpr int kMaxStages = 12;
@@ -82,7 +83,8 @@ static int dyn_smem_bytes(int tile_q, int stages, int cta_group, int tile_k) {
   const int staging0 = tile_q >= 64 ? 4 * 2 * 32 * 128 : 0;
   const int recv = tile_q <= 64 ? kTileP * tile_q * 4 : 0;
   const int staging = recv > staging0 ? recv : staging0;
-  return stages * (kTileP * tile_k * 2 + (tile_q / cta_group) * tile_k * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 32 + 1024;
+  const int bias = tile_q > 256 ? tile_q * 2 : 256 * 4;
+  return stages * (kTileP * tile_k * 2 + (tile_q / cta_group) * tile_k * 2) + staging + bias + (2 * stages + 4) * 8 + 32 + 1024;
 }
 
 struct DeviceInfo {
@@ -196,7 +198,7 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
   pl.stages = stages;
   pl.smem_bytes = dyn_smem_bytes(pl.tile_n, stages, pl.cta_group, pl.tile_k);
   pl.tmem_cols = 32;
-  while (pl.tmem_cols < 2 * pl.tile_n) pl.tmem_cols *= 2;  // allocated in powers of two
+  while (pl.tmem_cols < 2 * pl.tile_n && pl.tmem_cols < 512) pl.tmem_cols *= 2;  // powers of two; a 512-wide tile has one accumulator
 
   int sms = sm_count_hint;
   if (need_sm_count && sms <= 0) return B200_GEMM_ERR_LAUNCH;
@@ -397,6 +399,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
 
   GemmParams& p = h->params;
   memset(&p, 0, sizeof(p));
+  const int mma_n = pl.tile_n > 256 ? 256 : pl.tile_n;  // columns of one tcgen05.mma (a 512-wide tile issues two per K step)
   const void* u_ptr = pl.swap_ab ? pb : pa;
   const void* v_ptr = pl.swap_ab ? pa : pb;
   const int64_t u_ld = pl.swap_ab ? ldb : lda, v_ld = pl.swap_ab ? lda : ldb;
@@ -406,7 +409,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
     if (rc) return rc;
   }
   if (!v_cp) {
-    rc = encode_operand(&p.tmap_v, v_ptr, a->in_dtype, r.v_mn, r.Q, a->k, v_ld, pl.tile_n / pl.cta_group);
+    rc = encode_operand(&p.tmap_v, v_ptr, a->in_dtype, r.v_mn, r.Q, a->k, v_ld, mma_n / pl.cta_group);
     if (rc) return rc;
   }
   p.u_cp = u_cp, p.v_cp = v_cp;
@@ -458,7 +461,7 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   p.out_dtype = a->out_dtype;
   p.in_dtype = a->in_dtype;
   p.u_mn_major = r.u_mn, p.v_mn_major = r.v_mn;
-  p.idesc = make_idesc(a->in_dtype, r.u_mn, r.v_mn, pl.tile_m, pl.tile_n);
+  p.idesc = make_idesc(a->in_dtype, r.u_mn, r.v_mn, pl.tile_m, mma_n);
   make_desc(r.u_mn, &p.u_desc_hi, &p.u_desc_lo, &p.u_kstep);
   make_desc(r.v_mn, &p.v_desc_hi, &p.v_desc_lo, &p.v_kstep);
   p.wait_limit_ns = a->policy.wait_limit_us > 0 ? (unsigned long long)a->policy.wait_limit_us * 1000ull : kWaitLimitNs;
@@ -614,7 +617,7 @@ int b200_gemm_selftest(void* cuda_stream, int32_t* failed_case) {
       {128, 2, 1, 0, 0, 0, 0, 0, 1, 0}, {256, 2, 1, 0, 0, 0, 0, 1, 1, 0},  {128, 1, 1, 0, 0, 0, 64, 0, 0, 0},
       {64, 1, 3, 0, 0, 0, 0, 1, 1, 0},  {64, 1, 2, 2, 0, 0, 0, 0, 1, 0},   {128, 1, 1, 0, 1, 0, 0, 0, 1, 0},
       {16, 1, 1, 0, 0, 0, 0, 0, 1, 1},  {32, 1, 2, 2, 0, 0, 64, 1, 0, 1},  {16, 1, 4, 2, 0, 1, 0, 1, 1, 1},
-      {192, 2, 1, 0, 0, 0, 0, 0, 1, 1},
+      {192, 2, 1, 0, 0, 0, 0, 0, 1, 1}, {512, 2, 1, 0, 0, 0, 0, 0, 1, 0},  {512, 2, 2, 0, 0, 0, 0, 1, 1, 0},
   };
   if (failed_case) *failed_case = -1;
   void* scratch_v = nullptr;

@@ -175,6 +175,10 @@ template <int TILE_Q, int STAGES, int CG, int TK>
 struct SmemLayout {
   static constexpr int kSub = TK / kBoxK;  // 64-deep boxes per operand and stage
   static constexpr int kVRows = TILE_Q / CG;
+  // One tcgen05.mma covers at most 256 columns: a 512-wide tile takes two per K step, each reading kMmaVRows of this
+  // CTA's V rows (half h of the tile = columns 256h .. 256h+255 of the accumulator).
+  static constexpr int kHalves = TILE_Q > 256 ? 2 : 1;
+  static constexpr int kMmaVRows = kVRows / kHalves;
   static constexpr int kVBoxBytes = kVRows * kBoxK * 2;
   static constexpr int kUStageBytes = kSub * kUBoxBytes;
   static constexpr int kVStageBytes = kSub * kVBoxBytes;
@@ -190,8 +194,9 @@ struct SmemLayout {
   static constexpr int kRecvBytes = TILE_Q <= 64 ? kTileP * TILE_Q * 4 : 0;
   static constexpr int kStagingBytes = TILE_Q >= 64 ? 4 * 2 * kStageOutBytes : 0;
   static constexpr int kOutBytes = kRecvBytes > kStagingBytes ? kRecvBytes : kStagingBytes;
-  static constexpr int kBiasOff = kOutOff + kOutBytes;   // float[256]
-  static constexpr int kBarOff = kBiasOff + 256 * 4;     // full[S], empty[S], acc_full[2], acc_empty[2]
+  static constexpr int kBiasOff = kOutOff + kOutBytes;   // float[256]; a 512-wide tile keeps its slice in 16 bits
+  static constexpr int kBiasBytes = TILE_Q > 256 ? TILE_Q * 2 : 256 * 4;
+  static constexpr int kBarOff = kBiasOff + kBiasBytes;  // full[S], empty[S], acc_full[2], acc_empty[2]
   static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;  // tmem ptr, abort flag, last flag, epilogue verdict
   static constexpr int kTotal = kMiscOff + 32;
   static constexpr int kDynBytes = kTotal + 1024;  // slack for manual 1024-byte alignment
@@ -218,13 +223,14 @@ __device__ __forceinline__ void report_abort(const GemmParams& p, int role, int 
   }
 }
 
-// Add bias, cast and store one chunk of CW consecutive Q-columns of one P-row.
-template <int CW>
+// Add bias, cast and store one chunk of CW consecutive Q-columns of one P-row (BIAS_Q_DONE: the caller has already
+// added the per-column bias).
+template <int CW, bool BIAS_Q_DONE = false>
 __device__ __forceinline__ void finalize_chunk(const GemmParams& p, float (&v)[CW], int prow, int q0,
                                                const float* bias_q /* smem, chunk-local */, float bias_p) {
   if (prow >= p.P) return;
   if (!p.swap_out) {
-    if (p.bias != nullptr) {
+    if (!BIAS_Q_DONE && p.bias != nullptr) {
 #pragma unroll
       for (int i = 0; i < CW; ++i) v[i] += bias_q[i];
     }
@@ -296,12 +302,15 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
   constexpr int CW = TILE_Q >= 32 ? 32 : 16;  // columns per tcgen05.ld
   constexpr int NCHUNK = TILE_Q / CW;
   // TMEM is allocated in powers of two of at least 32 columns: two accumulators of TILE_Q columns each
+  // (a 512-wide tile fills all 512 columns with one accumulator: its epilogue does not overlap the next main loop)
+  constexpr int kAccBufs = 2 * TILE_Q <= 512 ? 2 : 1;
   constexpr uint32_t kTmemCols = 2 * TILE_Q <= 32 ? 32 : 2 * TILE_Q <= 64 ? 64 : 2 * TILE_Q <= 128 ? 128 : 2 * TILE_Q <= 256 ? 256 : 512;
   // a pair's two CTAs both report to the leader's barrier; with loader warps only the TMA-fetched operand counts
   const uint32_t tx_bytes = LOADER ? p.tma_tx_bytes : (uint32_t)(CG * L::kStageBytes);
   // arrivals that complete a stage: the producer's expect_tx, plus one per CTA from its loader warps
   constexpr uint32_t kFullArrivals = LOADER ? 1 + CG : 1;
   constexpr int kVRows = L::kVRows;
+  constexpr int kMmaVRows = L::kMmaVRows;
   constexpr int kSlotVec = NCHUNK * (CW / 4) * kTileP;  // float4 per partial slot of one CTA
 
   extern __shared__ uint8_t smem_raw[];
@@ -414,10 +423,14 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
           const int k0 = kb * TK + sub * kBoxK;
           const uint32_t bv = sv + sub * L::kVBoxBytes;
           if (!p.v_mn_major) {
-            load(bv, &p.tmap_v, k0, q0, fb);
-          } else {
 #pragma unroll
-            for (int j = 0; j < (kVRows >= 64 ? kVRows / 64 : 1); ++j) load(bv + 8192u * j, &p.tmap_v, q0 + 64 * j, k0, fb);
+            for (int h = 0; h < L::kHalves; ++h)
+              load(bv + (uint32_t)(h * kMmaVRows * 128), &p.tmap_v, k0, q0 + h * (CG * kMmaVRows), fb);
+          } else {
+            constexpr int kPerHalf = kMmaVRows >= 64 ? kMmaVRows / 64 : 1;  // 64-row boxes per accumulator half
+#pragma unroll
+            for (int j = 0; j < (kVRows >= 64 ? kVRows / 64 : 1); ++j)
+              load(bv + 8192u * j, &p.tmap_v, q0 + 64 * (j % kPerHalf) + (j / kPerHalf) * (CG * kMmaVRows), k0, fb);
           }
         }
       };
@@ -431,8 +444,12 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
 #pragma unroll 1
       for (; ok && wi.next(p, w); ++item) {
         const int u = w.tile;
-        const int p0 = (w.tp * CG + rank) * kTileP, q0 = w.tq * TILE_Q + rank * kVRows;
-        if (lane == 0) trace_stamp(p, 0, item, 0);
+        // the pair's MMA reads rows 0..kMmaVRows-1 of each CTA's V stage as columns rank * kMmaVRows .. of the accumulator
+        const int p0 = (w.tp * CG + rank) * kTileP, q0 = w.tq * TILE_Q + rank * kMmaVRows;
+        if (lane == 0) {
+          trace_stamp(p, 0, item, 0);
+          trace_value(p, 0, item, 3, clock64());  // with the epilogue's pair of the same kind: the SM clock of this run
+        }
 #pragma unroll 1
         for (int kj = 0; kj < w.kbn; ++kj) {
           const int kb = w.kb0 + kj * w.kstep;
@@ -504,8 +521,8 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
 #pragma unroll 1
       for (; ok && wi.next(p, w); ++it) {
         const int u = w.tile;
-        const int buf = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
+        const int buf = kAccBufs == 2 ? (it & 1) : 0;
+        const uint32_t acc_phase = (kAccBufs == 2 ? (it >> 1) : it) & 1;
         int good = 1;
         if (lane == 0) good = mbar_wait<CG == 2>(acce_bar(buf), acc_phase ^ 1u, abort_s, wait_limit) ? 1 : 0;
         good = __shfl_sync(0xffffffffu, good, 0);
@@ -552,8 +569,10 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
               const uint64_t dv = (uint64_t(p.v_desc_hi) << 32) | uint64_t(p.v_desc_lo | ((bv >> 4) & 0x3fffu));
 #pragma unroll
               for (int j = 0; j < kBoxK / kUmmaK; ++j) {
-                umma_f16<CG>(d_tmem, du + uint64_t(j * p.u_kstep), dv + uint64_t(j * p.v_kstep), p.idesc,
-                             (kb | sub | j) != 0 ? 1u : 0u);
+#pragma unroll
+                for (int h = 0; h < L::kHalves; ++h)
+                  umma_f16<CG>(d_tmem + (uint32_t)(h * 256), du + uint64_t(j * p.u_kstep),
+                               dv + uint64_t(j * p.v_kstep + h * ((kMmaVRows * 128) >> 4)), p.idesc, (kb | sub | j) != 0 ? 1u : 0u);
               }
             }
             if (tracing) c3 = clock64();
@@ -606,8 +625,8 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
 #pragma unroll 1
     for (; wi.next(p, w); ++it) {
       const int u = w.tile;
-      const int buf = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
+      const int buf = kAccBufs == 2 ? (it & 1) : 0;
+      const uint32_t acc_phase = (kAccBufs == 2 ? (it >> 1) : it) & 1;
       const int prow = (w.tp * CG + rank) * kTileP + row;
       const int qbase = w.tq * TILE_Q;
       const bool direct = !w.partial;
@@ -619,7 +638,10 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
           named_bar_sync(1, kEpiThreads);  // previous unit finished reading bias_s
           for (int i = et; i < TILE_Q; i += kEpiThreads) {
             const int q = qbase + i;
-            bias_s[i] = q < p.Q ? load_in_as_float(p.bias, q, p.in_dtype) : 0.f;
+            if constexpr (TILE_Q > 256)  // kept as the 16 input bits (zero bits are 0.0 in both formats)
+              reinterpret_cast<uint16_t*>(bias_s)[i] = q < p.Q ? reinterpret_cast<const uint16_t*>(p.bias)[q] : (uint16_t)0;
+            else
+              bias_s[i] = q < p.Q ? load_in_as_float(p.bias, q, p.in_dtype) : 0.f;
           }
           named_bar_sync(1, kEpiThreads);
         } else if (prow < p.P) {
@@ -686,7 +708,8 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
       // before rewriting it. In a CTA's last work item nothing will be loaded into the operand ring any more and the
       // accumulator being complete means the ring has been read: every flush then gets an image of its own in the ring
       // and never waits (the exposed epilogue at the end of the kernel is otherwise bound by TMA-store round trips).
-      constexpr int kFlushesPerTile = NCHUNK;  // at most one flush per chunk (fp32 output)
+      // at most one flush per chunk (fp32 output); a 512-wide tile of 16-bit output counts its real one per two chunks
+      const int kFlushesPerTile = (TILE_Q > 256 && p.out_dtype != 1) ? NCHUNK / 2 : NCHUNK;
       const bool tail_stage = L::kRingBytes >= 4 * kFlushesPerTile * L::kStageOutBytes && !wi.more(p);
       const uint32_t out_stage0 = tail_stage ? base + (uint32_t)(warp - 2) * (uint32_t)(kFlushesPerTile * L::kStageOutBytes)
                                              : base + L::kOutOff + (uint32_t)(warp - 2) * (2 * L::kStageOutBytes);
@@ -716,13 +739,42 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
       };
+      // Adds the bias of the CW columns of chunk c, from the 16-bit slice a 512-wide tile keeps.
+      auto add_bias16 = [&](int c, float(&v)[CW]) {
+        const uint4* s16 = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(bias_s) + c * CW);
+#pragma unroll
+        for (int j = 0; j < CW / 8; ++j) {
+          const uint4 x = s16[j];
+          const uint32_t wds[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            if (p.in_dtype == 2) {
+              v[8 * j + 2 * t] += __uint_as_float(wds[t] << 16);
+              v[8 * j + 2 * t + 1] += __uint_as_float(wds[t] & 0xffff0000u);
+            } else {
+              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wds[t]));
+              v[8 * j + 2 * t] += f.x, v[8 * j + 2 * t + 1] += f.y;
+            }
+          }
+        }
+      };
+      auto finalize = [&](float(&v)[CW], int c) {
+        if constexpr (TILE_Q > 256) {
+          if (p.bias != nullptr && !p.swap_out) add_bias16(c, v);
+          finalize_chunk<CW, true>(p, v, prow, qbase + c * CW, nullptr, bias_p);
+        } else {
+          finalize_chunk<CW>(p, v, prow, qbase + c * CW, bias_s + c * CW, bias_p);
+        }
+      };
       auto process_chunk = [&](uint32_t(&r)[32], int c) {
         float v[CW];
 #pragma unroll
         for (int i = 0; i < CW; ++i) v[i] = __uint_as_float(r[i]);
         if (staged) {
           if constexpr (CW == 32) {
-            if (p.bias != nullptr && !red) {  // in the atomic mode C already holds the bias
+            if constexpr (TILE_Q > 256) {
+              if (p.bias != nullptr && !red) add_bias16(c, v);
+            } else if (p.bias != nullptr && !red) {  // in the atomic mode C already holds the bias
               const float4* b4 = reinterpret_cast<const float4*>(bias_s + c * CW);  // 16-byte aligned: one load per 4 columns
 #pragma unroll
               for (int j = 0; j < CW / 4; ++j) {
@@ -769,7 +821,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
             }
           }
         } else if (direct) {
-          finalize_chunk<CW>(p, v, prow, qbase + c * CW, bias_s + c * CW, bias_p);
+          finalize(v, c);
         } else if (cluster_mode) {
           // cluster split-K: the partial sums of row r go to the CTA that owns r, into its image
           // recv[source rank][chunk][r % R][CW]. A lane holds one row, so the warp first transposes through its staging
@@ -883,7 +935,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
                 }
               }
             }
-            finalize_chunk<CW>(p, v, prow, qbase + c * CW, bias_s + c * CW, bias_p);
+            finalize(v, c);
           }
         }
         named_bar_sync(2, kEpiThreads);  // last_s may be rewritten by the next unit

@@ -20,7 +20,7 @@ constexpr KernelFn kfn() {
 
 KernelFn single_k128_variant(int tile_q, int stages);  // one CTA per tile, 128 K elements per stage: tile_n 16..128
 KernelFn single_k64_variant(int tile_q, int stages);   // one CTA per tile, 64 K elements per stage: tile_n 16..256
-KernelFn pair_variant(int tile_q, int stages);         // a CTA pair per 256-row tile: tile_n 128, 192, 256
+KernelFn pair_variant(int tile_q, int stages);         // a CTA pair per 256-row tile: tile_n 128, 192, 256, 512
 // Variants with cp.async loader warps, built at the deepest ring of each family only: `*stages` receives that depth.
 KernelFn loader_variant(int tile_q, int cta_group, int tile_k, int* stages);
 

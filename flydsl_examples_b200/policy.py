@@ -19,7 +19,7 @@ TILE_K = 64   # one TMA box: a 128-byte swizzle span of 16-bit data
 TILE_N_MENU = (16, 32, 64, 128, 256)
 MAX_STAGES = {16: 5, 32: 5, 64: 4, 128: 3, 256: 4}            # one CTA per tile, default stage depth
 MAX_STAGES_K64 = {16: 8, 32: 8, 64: 8, 128: 6, 256: 4}        # one CTA per tile, 64-deep stages
-MAX_STAGES_PAIR = {128: 8, 192: 6, 256: 6}                    # a CTA pair per 256-row tile (cta_group 2)
+MAX_STAGES_PAIR = {128: 8, 192: 6, 256: 6, 512: 4}            # a CTA pair per 256-row tile (cta_group 2)
 
 
 def tile_k(tile_n: int, cta_group: int = 1, requested: int = 0) -> int:
@@ -79,7 +79,8 @@ def smem_bytes(tile_n: int, stages: int, cta_group: int = 1, requested_tile_k: i
     staging = 4 * 2 * 32 * 128 if tile_n >= 64 else 0  # epilogue images for TMA stores
     staging = max(staging, TILE_M * tile_n * 4 if tile_n <= 64 else 0)  # rows received in cluster split-K mode
     tk = tile_k(tile_n, cta_group, requested_tile_k)
-    return stages * (TILE_M * tk * 2 + (tile_n // cta_group) * tk * 2) + staging + 256 * 4 + (2 * stages + 4) * 8 + 32 + 1024
+    bias = tile_n * 2 if tile_n > 256 else 256 * 4  # a 512-wide tile keeps its bias slice in 16 bits
+    return stages * (TILE_M * tk * 2 + (tile_n // cta_group) * tk * 2) + staging + bias + (2 * stages + 4) * 8 + 32 + 1024
 
 
 def split_k_slices(k: int, split_k: int, tk: int = TILE_K) -> list[tuple[int, int]]:
@@ -187,16 +188,17 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
     v_mn = a_mn if pol.swap_ab else b_mn
     if v_mn and (pol.tile_n // pol.cta_group) % 64 != 0:
         return "a tile_n-side operand that is not K-contiguous needs a multiple of 64 tile_n columns per CTA"
-    if 2 * pol.tile_n > TMEM_COLUMNS:
-        return "two accumulators do not fit in 512 TMEM columns"
+    if pol.tile_n > TMEM_COLUMNS:
+        return "the accumulator does not fit in 512 TMEM columns"
     return None
 
 
 # Rough cost of one 64-deep K block of a tile, in SM cycles, used only to rank candidate tilings. Two bounds, both
 # measured: the tensor pipe needs 128 cycles per 128 x 256 x 16 MMA, and one SM takes in about 64 bytes per clock
 # from L2, i.e. 2 * (128 + tile_n) cycles for the 128 + tile_n operand rows of a block (a CTA of a pair loads half of
-# the tile_n rows). Every single-CTA tile is bound by the second; the 256 x 256 pair balances the two.
-_KBLOCK_CYCLES = {(1, 256): 800.0, (2, 256): 590.0, (2, 192): 530.0, (1, 128): 540.0, (1, 64): 400.0, (1, 32): 340.0,
+# the tile_n rows). Every single-CTA tile is bound by the second; the 256 x 256 pair balances the two (its main loop
+# runs 8-15 % above the tensor time), the 256 x 512 pair is tensor-bound (3 % above).
+_KBLOCK_CYCLES = {(1, 256): 800.0, (2, 256): 590.0, (2, 512): 1060.0, (2, 192): 530.0, (1, 128): 540.0, (1, 64): 400.0, (1, 32): 340.0,
                   (1, 16): 310.0}
 _FIXED_CYCLES = 6000.0  # launch tail, pipeline fill, last epilogue
 
@@ -220,7 +222,9 @@ def _estimate_cycles(p_ext: int, q: int, kb: int, cta_group: int, tile_n: int, n
     tiles = -(-p_ext // (TILE_M * cta_group)) * -(-q // tile_n)
     split, _ = _auto_split(tiles, kb, walkers, cta_group == 1 and tile_n <= 64)
     waves = -(-(tiles * split) // walkers)
-    epilogue = 1000.0 + 500.0 * tile_n / 256
+    # per tile, outside the main loop: the hand-over between tiles; a 512-wide tile has a single accumulator, so its
+    # whole epilogue (about 8 us) stands between two main loops
+    epilogue = 12000.0 if tile_n > 256 else 1000.0 + 500.0 * tile_n / 256
     # after the main loop: a cluster exchange of a narrow tile costs about 1 us, a reduction through global memory
     # (partial write, fences and ticket, read-back) about 5 us
     # (the last arriver reads split slabs of 128 x tile_n floats at about 24 bytes per clock)
@@ -247,6 +251,8 @@ def heuristic(m: int, n: int, k: int, layout: str = "nt", num_sms: int = NUM_SMS
         cands = [(1, t) for t in menu if t <= max(64, 1 << (max(q, 1) - 1).bit_length())]
         if p_ext > TILE_M and q > 128:
             cands.append((2, 256))
+            if q > 256:
+                cands.append((2, 512))  # a quarter less operand traffic per flop; pays on many-wave problems with long K
             if not v_mn:
                 cands.append((2, 192))  # 96 columns per CTA: K-contiguous tile_n-side operand only
         best = min(cands, key=lambda c: (_estimate_cycles(p_ext, q, kb, c[0], c[1], num_sms), -c[1], -c[0]))

@@ -29,7 +29,7 @@ def test_version_variants_and_strerror():
     lib = _lib.load()
     assert b"sm_100a" in lib.b200_gemm_version()
     v = _lib.variants()
-    assert {x["tile_n"] for x in v} == {16, 32, 64, 128, 192, 256}
+    assert {x["tile_n"] for x in v} == {16, 32, 64, 128, 192, 256, 512}
     assert {(x["tile_n"], x["cta_group"], x["tile_k"]) for x in v} >= {(128, 1, 128), (128, 1, 64), (16, 1, 64), (256, 1, 64), (256, 2, 64)}
     assert _lib.strerror(0) == "ok"
     assert "policy" in _lib.strerror(-2)

@@ -316,6 +316,37 @@ def test_cta_pair_192_wide_tiles(dtype, idx):
         run_case(O.Case("pair192", dtype, "nn", m, n, k, seed=1, user_kwargs=kw))
 
 
+PAIR_512 = [  # 256 x 512 pair tiles: two MMAs per K step into one accumulator that fills TMEM
+    (512, 1024, 520, {"tile_n": 512, "cta_group": 2}),
+    (700, 900, 1000, {"tile_n": 512, "cta_group": 2}),                      # ragged in M and N, second half-tile partly empty
+    (300, 200, 328, {"tile_n": 512, "cta_group": 2}),                       # N inside the first accumulator half
+    (2048, 4096, 4096, {"tile_n": 512, "cta_group": 2}),                    # config 2's shape: 64 pair tiles, one wave
+    (2048, 4096, 1024, {"tile_n": 512, "cta_group": 2, "max_ctas": 32}),    # four tiles per pair: the accumulator is reused
+    (1000, 3000, 4100, {"tile_n": 512, "cta_group": 2, "stream_k": True}),
+    (512, 1024, 4096, {"tile_n": 512, "cta_group": 2, "split_k": 3}),
+    (2048, 2048, 512, {"tile_n": 512, "cta_group": 2, "group_m": 4, "stages": 3}),
+    (1024, 1024, 4096, {"tile_n": 512, "cta_group": 2, "split_k": 4, "split_mode": "atomic"}),
+]
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("idx", range(len(PAIR_512)))
+def test_cta_pair_512_wide_tiles(dtype, idx):
+    m, n, k, kw = PAIR_512[idx]
+    for layout in LAYOUTS:
+        for out_dtype in (None, "fp32"):
+            case = O.Case("pair512", dtype, layout, m, n, k, seed=470 + idx, bias_std=0.5, out_dtype=out_dtype, user_kwargs=kw)
+            run_case(case, repeats=2, prefill="randn")
+
+
+def test_pair_512_plan():
+    a = torch.empty(2048, 4096, dtype=torch.bfloat16, device=DEV)
+    b = torch.empty(4096, 4096, dtype=torch.bfloat16, device=DEV).t()
+    pl = plan(a, b, "nt", {"tile_n": 512, "cta_group": 2})
+    assert (pl["tile_m"], pl["tile_n"], pl["tmem_cols"], pl["stages"], pl["grid"]) == (256, 512, 512, 4, 128)
+    assert pl["smem_bytes"] <= 232448
+
+
 def test_default_policy_picks_a_pair_for_large_shapes():
     a = torch.empty(8192, 4096, dtype=torch.bfloat16, device=DEV)
     b = torch.empty(4096, 4096, dtype=torch.bfloat16, device=DEV).t()

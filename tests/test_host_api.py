@@ -119,11 +119,18 @@ def test_validate_rules():
     assert P.validate(P.Policy(tile_n=256, tile_k=128), 512, 512, 512, "nt") is not None
     assert P.validate(P.Policy(tile_n=64, tile_k=64), 512, 512, 512, "nt") is None
     assert (P.max_stages(128), P.max_stages(128, 1, 64), P.max_stages(128, 2)) == (3, 6, 8)
+    # 512 columns: one accumulator that fills TMEM, CTA pairs only, four 48 KB stages
+    assert P.validate(P.Policy(tile_n=512), 512, 1024, 512, "nt") is not None
+    assert P.validate(P.Policy(tile_n=512, cta_group=2), 512, 1024, 512, "nt") is None
+    assert P.validate(P.Policy(tile_n=512, cta_group=2), 512, 1024, 512, "nn") is None
+    assert P.validate(P.Policy(tile_n=512, cta_group=2, split_k=2, split_mode="cluster"), 512, 1024, 512, "nt") is not None
+    assert P.max_stages(512, 2) == 4 and P.smem_bytes(512, 5, 2) > P.SMEM_LIMIT
 
 
 def test_heuristic_is_always_valid():
     shapes = [(1, 5120, 2880), (3, 32, 256), (32, 384, 7168), (256, 512, 1024), (2048, 4096, 4096), (1000, 3000, 4100),
-              (16384, 28672, 8192), (16384, 3584, 8192), (65, 96, 192), (4096, 128, 6144), (8, 7168, 2048)]
+              (16384, 28672, 8192), (16384, 3584, 8192), (65, 96, 192), (4096, 128, 6144), (8, 7168, 2048), (8192, 8192, 8192),
+              (6000, 6000, 6000)]
     for m, n, k in shapes:
         for layout in ("nn", "nt", "tn", "tt"):
             pol = P.heuristic(m, n, k, layout)
@@ -171,6 +178,11 @@ def test_plan_query_on_cpu_tensors():
               {"tile_n": 32, "swap_ab": True, "split_k": 16}, out_dtype=torch.float32)
     assert pl["swap_ab"] == 1 and pl["tiles_p"] == 3 and pl["tiles_q"] == 1 and pl["num_units"] == 48
     assert pl["partial_bytes"] == 48 * 128 * 32 * 4 and pl["counter_bytes"] == 1 << 20
+    plw = plan(a, b, "nt", {"tile_n": 512, "cta_group": 2})
+    assert (plw["tile_m"], plw["tile_n"], plw["stages"], plw["tmem_cols"], plw["grid"]) == (256, 512, 4, 512, 128)
+    assert plw["smem_bytes"] == P.smem_bytes(512, 4, 2) <= P.SMEM_LIMIT
+    with pytest.raises(RuntimeError, match="unsupported policy"):
+        plan(a, b, "nt", {"tile_n": 512})
     # split_k larger than the number of K blocks (128 deep for this tile) is clamped
     pl = plan(torch.empty(64, 300, dtype=torch.float16), torch.empty(300, 64, dtype=torch.float16), "nn", {"tile_n": 64, "split_k": 9})
     assert pl["split_k"] == 3
