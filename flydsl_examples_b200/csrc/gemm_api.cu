@@ -71,7 +71,13 @@ static KernelFn variant_fn(const Variant& v, int stages) {
   return v.tile_k == 128 ? single_k128_variant(v.tile_q, stages) : single_k64_variant(v.tile_q, stages);
 }
 
+// The 512-column pair variant takes the width of its tiles at run time: any multiple of 32 above 256.
+static int variant_width(int tile_n, int cta_group) {
+  return (cta_group == 2 && tile_n > 256 && tile_n <= 512 && tile_n % 32 == 0) ? 512 : tile_n;
+}
+
 static const Variant* find_variant(int tile_q, int cta_group, int tile_k) {
+  tile_q = variant_width(tile_q, cta_group);
   for (int i = 0; i < kNumVariants; ++i)
     if (kVariants[i].tile_q == tile_q && kVariants[i].cta_group == cta_group &&
         (tile_k == 0 || kVariants[i].tile_k == tile_k))
@@ -179,7 +185,7 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
     r->u_mn = b_mn, r->v_mn = a_mn;
   }
   // an MN-major operand is fetched in boxes 64 elements wide: each CTA's share of tile_n must be whole boxes
-  if (r->v_mn && (pl.tile_n / pl.cta_group) % 64 != 0) return B200_GEMM_ERR_BAD_POLICY;
+  if (r->v_mn && (var->tile_q / pl.cta_group) % 64 != 0) return B200_GEMM_ERR_BAD_POLICY;
 
   pl.tiles_p = (r->P + pl.tile_m - 1) / pl.tile_m;
   pl.tiles_q = (r->Q + pl.tile_n - 1) / pl.tile_n;
@@ -196,9 +202,9 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
   if (stages < 2) return B200_GEMM_ERR_BAD_POLICY;
   if (pl.a_loader || pl.b_loader) loader_variant(pl.tile_n, pl.cta_group, var->tile_k, &stages);  // one depth is built
   pl.stages = stages;
-  pl.smem_bytes = dyn_smem_bytes(pl.tile_n, stages, pl.cta_group, pl.tile_k);
+  pl.smem_bytes = dyn_smem_bytes(var->tile_q, stages, pl.cta_group, pl.tile_k);
   pl.tmem_cols = 32;
-  while (pl.tmem_cols < 2 * pl.tile_n && pl.tmem_cols < 512) pl.tmem_cols *= 2;  // powers of two; a 512-wide tile has one accumulator
+  while (pl.tmem_cols < 2 * var->tile_q && pl.tmem_cols < 512) pl.tmem_cols *= 2;  // powers of two; a 512-column variant has one accumulator
 
   int sms = sm_count_hint;
   if (need_sm_count && sms <= 0) return B200_GEMM_ERR_LAUNCH;
@@ -271,8 +277,8 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
   // ever writes partial sums or a repack image where another call keeps its tickets.
   pl.counter_bytes = (tickets || pl.a_repacked || pl.b_repacked) ? kCounterBytes : 0;
   pl.partial_bytes = pl.atomic_out   ? 0
-                     : pl.sk_tiles > 0 ? (uint64_t)pl.sk_tiles * pl.sk_slots * pl.tile_m * pl.tile_n * 4
-                     : (pl.split_k > 1 && pl.cluster_split == 0) ? (uint64_t)pl.num_units * pl.tile_m * pl.tile_n * 4
+                     : pl.sk_tiles > 0 ? (uint64_t)pl.sk_tiles * pl.sk_slots * pl.tile_m * var->tile_q * 4
+                     : (pl.split_k > 1 && pl.cluster_split == 0) ? (uint64_t)pl.num_units * pl.tile_m * var->tile_q * 4
                                                                  : 0;
   const uint64_t ra = pl.a_repacked ? round_up((uint64_t)a_rows * r->ra_ld * 2, 256) : 0;
   const uint64_t rb = pl.b_repacked ? round_up((uint64_t)b_rows * r->rb_ld * 2, 256) : 0;
@@ -462,6 +468,8 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   p.in_dtype = a->in_dtype;
   p.u_mn_major = r.u_mn, p.v_mn_major = r.v_mn;
   p.idesc = make_idesc(a->in_dtype, r.u_mn, r.v_mn, pl.tile_m, mma_n);
+  p.idesc2 = pl.tile_n > 256 ? make_idesc(a->in_dtype, r.u_mn, r.v_mn, pl.tile_m, pl.tile_n - 256) : 0;
+  p.tile_q = pl.tile_n;
   make_desc(r.u_mn, &p.u_desc_hi, &p.u_desc_lo, &p.u_kstep);
   make_desc(r.v_mn, &p.v_desc_hi, &p.v_desc_lo, &p.v_kstep);
   p.wait_limit_ns = a->policy.wait_limit_us > 0 ? (unsigned long long)a->policy.wait_limit_us * 1000ull : kWaitLimitNs;
@@ -618,6 +626,7 @@ int b200_gemm_selftest(void* cuda_stream, int32_t* failed_case) {
       {64, 1, 3, 0, 0, 0, 0, 1, 1, 0},  {64, 1, 2, 2, 0, 0, 0, 0, 1, 0},   {128, 1, 1, 0, 1, 0, 0, 0, 1, 0},
       {16, 1, 1, 0, 0, 0, 0, 0, 1, 1},  {32, 1, 2, 2, 0, 0, 64, 1, 0, 1},  {16, 1, 4, 2, 0, 1, 0, 1, 1, 1},
       {192, 2, 1, 0, 0, 0, 0, 0, 1, 1}, {512, 2, 1, 0, 0, 0, 0, 0, 1, 0},  {512, 2, 2, 0, 0, 0, 0, 1, 1, 0},
+      {352, 2, 1, 0, 0, 0, 0, 0, 1, 0},
   };
   if (failed_case) *failed_case = -1;
   void* scratch_v = nullptr;

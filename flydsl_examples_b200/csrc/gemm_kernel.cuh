@@ -64,6 +64,8 @@ struct alignas(64) GemmParams {
   int u_mn_major;   // 1: U is P-contiguous, loaded as two [64 P x 64 K] boxes
   int v_mn_major;   // 1: V is Q-contiguous, loaded as TILE_Q/64 boxes
   uint32_t idesc;   // tcgen05 instruction descriptor
+  uint32_t idesc2;  // 512-column variant: descriptor of the second MMA of a K step (N = tile_q - 256)
+  int tile_q;       // 512-column variant: columns of one tile, 288..512 in steps of 32 (the other variants use TILE_Q)
   uint32_t u_desc_hi, u_desc_lo;  // smem matrix descriptor without the start address
   uint32_t v_desc_hi, v_desc_lo;
   uint32_t u_kstep, v_kstep;  // start-address increment (16-byte units) per K=16 MMA inside a stage
@@ -301,6 +303,11 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
   using L = SmemLayout<TILE_Q, STAGES, CG, TK>;
   constexpr int CW = TILE_Q >= 32 ? 32 : 16;  // columns per tcgen05.ld
   constexpr int NCHUNK = TILE_Q / CW;
+  // The 512-column variant takes the width of its tiles at run time (a multiple of 32 above 256): the host picks the
+  // width that fills whole waves. Its second MMA then covers tile_q - 256 columns, read from the first
+  // (tile_q - 256) / 2 rows of each CTA's second V box; the boxes themselves are always loaded whole.
+  const int tile_q = TILE_Q > 256 ? p.tile_q : TILE_Q;
+  const int nchunk = TILE_Q > 256 ? tile_q / CW : NCHUNK;
   // TMEM is allocated in powers of two of at least 32 columns: two accumulators of TILE_Q columns each
   // (a 512-wide tile fills all 512 columns with one accumulator: its epilogue does not overlap the next main loop)
   constexpr int kAccBufs = 2 * TILE_Q <= 512 ? 2 : 1;
@@ -422,15 +429,17 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
         for (int sub = 0; sub < L::kSub; ++sub) {
           const int k0 = kb * TK + sub * kBoxK;
           const uint32_t bv = sv + sub * L::kVBoxBytes;
+          // first V row of accumulator half h: q0 for half 0; half 1 starts 256 columns into the tile and gives each
+          // CTA (tile_q - 256) / 2 of its columns
+          auto half_q0 = [&](int h) { return h == 0 ? q0 : q0 - rank * kMmaVRows + 256 + rank * ((tile_q - 256) >> 1); };
           if (!p.v_mn_major) {
 #pragma unroll
-            for (int h = 0; h < L::kHalves; ++h)
-              load(bv + (uint32_t)(h * kMmaVRows * 128), &p.tmap_v, k0, q0 + h * (CG * kMmaVRows), fb);
+            for (int h = 0; h < L::kHalves; ++h) load(bv + (uint32_t)(h * kMmaVRows * 128), &p.tmap_v, k0, half_q0(h), fb);
           } else {
             constexpr int kPerHalf = kMmaVRows >= 64 ? kMmaVRows / 64 : 1;  // 64-row boxes per accumulator half
 #pragma unroll
             for (int j = 0; j < (kVRows >= 64 ? kVRows / 64 : 1); ++j)
-              load(bv + 8192u * j, &p.tmap_v, q0 + 64 * (j % kPerHalf) + (j / kPerHalf) * (CG * kMmaVRows), k0, fb);
+              load(bv + 8192u * j, &p.tmap_v, half_q0(j / kPerHalf) + 64 * (j % kPerHalf), k0, fb);
           }
         }
       };
@@ -445,7 +454,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
       for (; ok && wi.next(p, w); ++item) {
         const int u = w.tile;
         // the pair's MMA reads rows 0..kMmaVRows-1 of each CTA's V stage as columns rank * kMmaVRows .. of the accumulator
-        const int p0 = (w.tp * CG + rank) * kTileP, q0 = w.tq * TILE_Q + rank * kMmaVRows;
+        const int p0 = (w.tp * CG + rank) * kTileP, q0 = w.tq * tile_q + rank * kMmaVRows;
         if (lane == 0) {
           trace_stamp(p, 0, item, 0);
           trace_value(p, 0, item, 3, clock64());  // with the epilogue's pair of the same kind: the SM clock of this run
@@ -572,7 +581,8 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
 #pragma unroll
                 for (int h = 0; h < L::kHalves; ++h)
                   umma_f16<CG>(d_tmem + (uint32_t)(h * 256), du + uint64_t(j * p.u_kstep),
-                               dv + uint64_t(j * p.v_kstep + h * ((kMmaVRows * 128) >> 4)), p.idesc, (kb | sub | j) != 0 ? 1u : 0u);
+                               dv + uint64_t(j * p.v_kstep + h * ((kMmaVRows * 128) >> 4)), h == 0 ? p.idesc : p.idesc2,
+                               (kb | sub | j) != 0 ? 1u : 0u);
               }
             }
             if (tracing) c3 = clock64();
@@ -628,7 +638,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
       const int buf = kAccBufs == 2 ? (it & 1) : 0;
       const uint32_t acc_phase = (kAccBufs == 2 ? (it >> 1) : it) & 1;
       const int prow = (w.tp * CG + rank) * kTileP + row;
-      const int qbase = w.tq * TILE_Q;
+      const int qbase = w.tq * tile_q;
       const bool direct = !w.partial;
 
       // Stage the bias slice of this tile (columns of D) while the main loop runs.
@@ -636,7 +646,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
       if (p.bias != nullptr) {
         if (!p.swap_out) {
           named_bar_sync(1, kEpiThreads);  // previous unit finished reading bias_s
-          for (int i = et; i < TILE_Q; i += kEpiThreads) {
+          for (int i = et; i < tile_q; i += kEpiThreads) {
             const int q = qbase + i;
             if constexpr (TILE_Q > 256)  // kept as the 16 input bits (zero bits are 0.0 in both formats)
               reinterpret_cast<uint16_t*>(bias_s)[i] = q < p.Q ? reinterpret_cast<const uint16_t*>(p.bias)[q] : (uint16_t)0;
@@ -709,7 +719,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
       // accumulator being complete means the ring has been read: every flush then gets an image of its own in the ring
       // and never waits (the exposed epilogue at the end of the kernel is otherwise bound by TMA-store round trips).
       // at most one flush per chunk (fp32 output); a 512-wide tile of 16-bit output counts its real one per two chunks
-      const int kFlushesPerTile = (TILE_Q > 256 && p.out_dtype != 1) ? NCHUNK / 2 : NCHUNK;
+      const int kFlushesPerTile = (TILE_Q > 256 && p.out_dtype != 1) ? (nchunk + 1) / 2 : nchunk;
       const bool tail_stage = L::kRingBytes >= 4 * kFlushesPerTile * L::kStageOutBytes && !wi.more(p);
       const uint32_t out_stage0 = tail_stage ? base + (uint32_t)(warp - 2) * (uint32_t)(kFlushesPerTile * L::kStageOutBytes)
                                              : base + L::kOutOff + (uint32_t)(warp - 2) * (2 * L::kStageOutBytes);
@@ -770,7 +780,10 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
         float v[CW];
 #pragma unroll
         for (int i = 0; i < CW; ++i) v[i] = __uint_as_float(r[i]);
-        if (staged) {
+        // an odd number of chunks (512-column variant): the last one has no partner to fill a 128-byte row of 16-bit
+        // output with, and leaves through the direct path
+        const bool lone = TILE_Q > 256 && p.out_dtype != 1 && c == nchunk - 1 && (c & 1) == 0;
+        if (staged && !lone) {
           if constexpr (CW == 32) {
             if constexpr (TILE_Q > 256) {
               if (p.bias != nullptr && !red) add_bias16(c, v);
@@ -868,20 +881,20 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
         load_chunk(ra, 0);
         tmem_ld_wait();
 #pragma unroll 1
-        for (int c = 0; c < NCHUNK; c += 2) {
-          if (c + 1 < NCHUNK)
+        for (int c = 0; c < nchunk; c += 2) {
+          if (c + 1 < nchunk)
             load_chunk(rb, c + 1);
           else
             release_acc();
           process_chunk(ra, c);
-          if (c + 1 < NCHUNK) {
+          if (c + 1 < nchunk) {
             tmem_ld_wait();
-            if (c + 2 < NCHUNK)
+            if (c + 2 < nchunk)
               load_chunk(ra, c + 2);
             else
               release_acc();
             process_chunk(rb, c + 1);
-            if (c + 2 < NCHUNK) tmem_ld_wait();
+            if (c + 2 < nchunk) tmem_ld_wait();
           }
         }
       }
@@ -907,7 +920,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
           const float4* tp0 = reinterpret_cast<const float4*>(p.partials) + (size_t)(w.slot0 * CG + rank) * kSlotVec + row;
           constexpr int kBatch = 4;  // contributors whose loads are in flight together
 #pragma unroll 1
-          for (int c = 0; c < NCHUNK; ++c) {
+          for (int c = 0; c < nchunk; ++c) {
             float v[CW];
 #pragma unroll
             for (int i = 0; i < CW; ++i) v[i] = 0.f;

@@ -31,9 +31,15 @@ def tile_k(tile_n: int, cta_group: int = 1, requested: int = 0) -> int:
     return 64
 
 
+def variant_width(tile_n: int, cta_group: int = 1) -> int:
+    """Width of the kernel variant that runs tiles of tile_n columns: the 512-column pair variant takes its tile
+    width at run time (any multiple of 32 above 256), every other variant has exactly one width."""
+    return 512 if (cta_group == 2 and 256 < tile_n <= 512 and tile_n % 32 == 0) else tile_n
+
+
 def max_stages(tile_n: int, cta_group: int = 1, requested_tile_k: int = 0) -> int:
     if cta_group == 2:
-        return MAX_STAGES_PAIR[tile_n]
+        return MAX_STAGES_PAIR[variant_width(tile_n, 2)]
     return (MAX_STAGES_K64 if tile_k(tile_n, 1, requested_tile_k) == 64 else MAX_STAGES)[tile_n]
 SMEM_LIMIT = 232448
 TMEM_COLUMNS = 512
@@ -76,6 +82,7 @@ class Policy:
 def smem_bytes(tile_n: int, stages: int, cta_group: int = 1, requested_tile_k: int = 0) -> int:
     """Dynamic shared memory of one CTA: the ring, the bias slice, the barriers and alignment slack. In a pair
     each CTA holds 128 of the tile's 256 rows and half of its tile_n columns."""
+    tile_n = variant_width(tile_n, cta_group)  # shared memory is laid out for the variant's full width
     staging = 4 * 2 * 32 * 128 if tile_n >= 64 else 0  # epilogue images for TMA stores
     staging = max(staging, TILE_M * tile_n * 4 if tile_n <= 64 else 0)  # rows received in cluster split-K mode
     tk = tile_k(tile_n, cta_group, requested_tile_k)
@@ -155,13 +162,15 @@ def stream_k_walk(cta: int, grid: int, tiles: int, kb_total: int, sk_tiles: int)
 
 def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
     """Return None when the policy is runnable for this problem, else the reason."""
-    if pol.tile_n not in TILE_N_MENU and not (pol.cta_group == 2 and pol.tile_n in MAX_STAGES_PAIR):
-        return f"tile_n must be one of {TILE_N_MENU} (or {tuple(MAX_STAGES_PAIR)} with cta_group 2), got {pol.tile_n}"
+    width = variant_width(pol.tile_n, pol.cta_group)
+    if pol.tile_n not in TILE_N_MENU and not (pol.cta_group == 2 and width in MAX_STAGES_PAIR):
+        return (f"tile_n must be one of {TILE_N_MENU} (or {tuple(MAX_STAGES_PAIR)} or a multiple of 32 between 288 and 512 "
+                f"with cta_group 2), got {pol.tile_n}")
     if pol.cta_group not in (1, 2):
         return f"cta_group must be 1 or 2, got {pol.cta_group}"
     stage_menu = MAX_STAGES if pol.cta_group == 1 else MAX_STAGES_PAIR
-    if pol.tile_n not in stage_menu:
-        return f"cta_group 2 needs tile_n in {tuple(MAX_STAGES_PAIR)}, got {pol.tile_n}"
+    if width not in stage_menu:
+        return f"cta_group 2 needs tile_n in {tuple(MAX_STAGES_PAIR)} (or a multiple of 32 between 288 and 512), got {pol.tile_n}"
     if pol.stages < 0 or pol.stages == 1:
         return f"stages must be 0 (auto) or >= 2, got {pol.stages} (more than fit are clamped)"
     if pol.tile_k not in (0, tile_k(pol.tile_n, pol.cta_group, pol.tile_k)):
@@ -186,7 +195,7 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
     a_mn = layout[0] == "t"
     b_mn = layout[1] == "n"
     v_mn = a_mn if pol.swap_ab else b_mn
-    if v_mn and (pol.tile_n // pol.cta_group) % 64 != 0:
+    if v_mn and (width // pol.cta_group) % 64 != 0:
         return "a tile_n-side operand that is not K-contiguous needs a multiple of 64 tile_n columns per CTA"
     if pol.tile_n > TMEM_COLUMNS:
         return "the accumulator does not fit in 512 TMEM columns"

@@ -326,6 +326,14 @@ PAIR_512 = [  # 256 x 512 pair tiles: two MMAs per K step into one accumulator t
     (512, 1024, 4096, {"tile_n": 512, "cta_group": 2, "split_k": 3}),
     (2048, 2048, 512, {"tile_n": 512, "cta_group": 2, "group_m": 4, "stages": 3}),
     (1024, 1024, 4096, {"tile_n": 512, "cta_group": 2, "split_k": 4, "split_mode": "atomic"}),
+    # widths chosen at run time: any multiple of 32 above 256 (an odd number of 32-column chunks when not a multiple of 64)
+    (2048, 4096, 4096, {"tile_n": 480, "cta_group": 2}),                    # config 2 as 72 tiles for 74 pairs
+    (512, 1024, 520, {"tile_n": 288, "cta_group": 2}),
+    (700, 900, 1000, {"tile_n": 352, "cta_group": 2}),
+    (1000, 3000, 1100, {"tile_n": 416, "cta_group": 2, "stream_k": True}),
+    (512, 960, 4096, {"tile_n": 320, "cta_group": 2, "split_k": 3}),
+    (1024, 1344, 2048, {"tile_n": 448, "cta_group": 2, "split_k": 2, "split_mode": "atomic"}),
+    (2048, 1536, 512, {"tile_n": 384, "cta_group": 2, "group_m": 4, "stages": 3, "max_ctas": 16}),
 ]
 
 
