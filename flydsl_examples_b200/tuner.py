@@ -48,6 +48,9 @@ def candidate_configs(args: TuneArgs, num_sms: int = P.NUM_SMS_DEFAULT) -> list[
     """Every runnable policy worth timing for this problem."""
     variants = [(1, t, tk) for t in P.TILE_N_MENU for tk in ((64, 128) if t <= 128 else (64,))]
     variants += [(2, t, 64) for t in P.MAX_STAGES_PAIR]
+    # run-time widths of the 512-column pair variant: worth timing where whole waves matter (few tiles per CTA pair)
+    if args.m > 2 * P.TILE_M and -(-args.m // (2 * P.TILE_M)) * -(-args.n // 256) <= 6 * (num_sms // 2):
+        variants += [(2, t, 64) for t in range(288, 512, 32)]
     out = []
     for (cg, tile_n, tk), swap in itertools.product(variants, (False, True)):
         if swap and (cg == 2 or args.m > 256):

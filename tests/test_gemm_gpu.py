@@ -347,6 +347,32 @@ def test_cta_pair_512_wide_tiles(dtype, idx):
             run_case(case, repeats=2, prefill="randn")
 
 
+@pytest.mark.parametrize("width", [512, 480, 352, 288])
+def test_pair_512_other_exits(width):
+    """The wide pair variant away from its TMA-store path: D written transposed (swap_ab, bias along the rows), C rows that
+    are not 16-byte aligned (direct vector / scalar stores, including the lone last chunk of an odd chunk count),
+    operands that need the aligned copy first, and exact small integers (a misplaced accumulator half or V box shows as
+    a wrong integer)."""
+    kw = {"tile_n": width, "cta_group": 2}
+    run_case(O.Case("wide_swap", "bf16", "nt", 600, 520, 700, seed=31, bias_std=0.5, user_kwargs={**kw, "swap_ab": True}), repeats=2)
+    run_case(O.Case("wide_swap32", "fp16", "tn", 600, 520, 700, seed=32, bias_std=0.5, out_dtype="fp32", user_kwargs={**kw, "swap_ab": True}))
+    run_case(O.Case("wide_pad", "bf16", "nt", 520, 1000, 333, seed=33, bias_std=0.5, pad=3, offset=1, user_kwargs=kw))
+    # C rows that are not 16-byte aligned (N odd): no TMA stores
+    for out_dtype in (None, "fp32"):
+        run_case(O.Case("wide_oddc", "bf16", "nt", 520, 1031, 520, seed=34, bias_std=0.5, out_dtype=out_dtype, user_kwargs=kw), repeats=2)
+    g = torch.Generator().manual_seed(width)
+    m, n, k = 512, 2 * width + 40, 1100
+    a_l = torch.randint(-2, 3, (m, k), generator=g).to(torch.bfloat16)
+    b_l = torch.randint(-2, 3, (k, n), generator=g).to(torch.bfloat16)
+    ref = (a_l.double() @ b_l.double()).float()
+    for layout in LAYOUTS:
+        a = O.place(a_l, layout[0] == "t", 0, 0, DEV)
+        b = O.place(b_l, layout[1] == "t", 0, 0, DEV)
+        got = gemm_a16w16(a, b, layout=layout, out_dtype=torch.float32, user_kwargs=kw)
+        check_status()
+        assert torch.equal(got.cpu(), ref), (layout, kw)
+
+
 def test_pair_512_plan():
     a = torch.empty(2048, 4096, dtype=torch.bfloat16, device=DEV)
     b = torch.empty(4096, 4096, dtype=torch.bfloat16, device=DEV).t()
