@@ -750,7 +750,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
         __syncwarp();
       };
       // Adds the bias of the CW columns of chunk c, from the 16-bit slice a 512-wide tile keeps.
-      auto add_bias16 = [&](int c, float(&v)[CW]) {
+      auto add_bias16 = [&](int c, auto& v, int off) {  // v[off .. off + CW) are the chunk's values
         const uint4* s16 = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(bias_s) + c * CW);
 #pragma unroll
         for (int j = 0; j < CW / 8; ++j) {
@@ -759,18 +759,18 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
             if (p.in_dtype == 2) {
-              v[8 * j + 2 * t] += __uint_as_float(wds[t] << 16);
-              v[8 * j + 2 * t + 1] += __uint_as_float(wds[t] & 0xffff0000u);
+              v[off + 8 * j + 2 * t] += __uint_as_float(wds[t] << 16);
+              v[off + 8 * j + 2 * t + 1] += __uint_as_float(wds[t] & 0xffff0000u);
             } else {
               const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wds[t]));
-              v[8 * j + 2 * t] += f.x, v[8 * j + 2 * t + 1] += f.y;
+              v[off + 8 * j + 2 * t] += f.x, v[off + 8 * j + 2 * t + 1] += f.y;
             }
           }
         }
       };
       auto finalize = [&](float(&v)[CW], int c) {
         if constexpr (TILE_Q > 256) {
-          if (p.bias != nullptr && !p.swap_out) add_bias16(c, v);
+          if (p.bias != nullptr && !p.swap_out) add_bias16(c, v, 0);
           finalize_chunk<CW, true>(p, v, prow, qbase + c * CW, nullptr, bias_p);
         } else {
           finalize_chunk<CW>(p, v, prow, qbase + c * CW, bias_s + c * CW, bias_p);
@@ -786,7 +786,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
         if (staged && !lone) {
           if constexpr (CW == 32) {
             if constexpr (TILE_Q > 256) {
-              if (p.bias != nullptr && !red) add_bias16(c, v);
+              if (p.bias != nullptr && !red) add_bias16(c, v, 0);
             } else if (p.bias != nullptr && !red) {  // in the atomic mode C already holds the bias
               const float4* b4 = reinterpret_cast<const float4*>(bias_s + c * CW);  // 16-byte aligned: one load per 4 columns
 #pragma unroll
@@ -876,8 +876,74 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
             __stcg(dst + j * kTileP, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
         }
       };
-      {
-        uint32_t ra[32], rb[32];
+      bool done = false;
+      uint32_t ra[32], rb[32];  // two register buffers for tcgen05.ld
+      if constexpr (TILE_Q > 256) {
+        // The single accumulator of this variant leaves its epilogue unhidden, so the common exit (whole tile, 16-bit
+        // output, TMA stores) takes 64 columns per step in one straight-line block: two tcgen05.ld, one wait, bias,
+        // cast, the lane's 128-byte row segment into the warp's swizzled staging image, one flush. The loads of the
+        // next step are issued once this step's values have left the registers and fly during the flush.
+        if (staged && !red && p.out_dtype != 1) {
+          done = true;
+          const int nstep = nchunk >> 1;
+          const bool lone = (nchunk & 1) != 0;  // a run-time width may leave one last chunk without a partner
+          load_chunk(ra, 0);
+          load_chunk(rb, 1);
+#pragma unroll 1
+          for (int sp = 0; sp < nstep; ++sp) {
+            tmem_ld_wait();
+            const bool more = sp + 1 < nstep;
+            if (!more && !lone) release_acc();
+            uint32_t pk[32];
+            auto half = [&](uint32_t(&r)[32], int h) {  // 32 columns: bias, cast, pack into pk[16h .. 16h + 16)
+              float v[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+              if (p.bias != nullptr) add_bias16(2 * sp + h, v, 0);
+              if (p.out_dtype == 2) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                  __nv_bfloat162 x = __floats2bfloat162_rn(v[i], v[i + 1]);
+                  pk[16 * h + i / 2] = *reinterpret_cast<uint32_t*>(&x);
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                  __half2 x = __floats2half2_rn(v[i], v[i + 1]);
+                  pk[16 * h + i / 2] = *reinterpret_cast<uint32_t*>(&x);
+                }
+              }
+            };
+            half(ra, 0);
+            half(rb, 1);
+            stage_acquire();
+            const uint32_t row_base = stage_image() + (uint32_t)lane * 128u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t addr = row_base + (uint32_t)((j ^ (lane & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * j]), "r"(pk[4 * j + 1]), "r"(pk[4 * j + 2]),
+                           "r"(pk[4 * j + 3])
+                           : "memory");
+            }
+            if (more) {
+              load_chunk(ra, 2 * sp + 2);
+              load_chunk(rb, 2 * sp + 3);
+            } else if (lone) {
+              load_chunk(ra, nchunk - 1);
+            }
+            stage_flush(qbase + sp * 64);
+          }
+          if (lone) {  // no partner to fill a 128-byte row with: direct stores
+            tmem_ld_wait();
+            release_acc();
+            float v[CW];
+#pragma unroll
+            for (int i = 0; i < CW; ++i) v[i] = __uint_as_float(ra[i]);
+            finalize(v, nchunk - 1);
+          }
+        }
+      }
+      if (!done) {
         load_chunk(ra, 0);
         tmem_ld_wait();
 #pragma unroll 1
