@@ -12,6 +12,8 @@ aligned, 't' A with M not divisible by 8, and any K (K tails) all run. Pass
 """
 from __future__ import annotations
 
+import dataclasses
+
 import ctypes as C
 import threading
 from collections import OrderedDict
@@ -147,17 +149,25 @@ def _strict_k_checks(k: int, kwargs: dict) -> None:
 
 
 def resolve_policy(m: int, n: int, k: int, dtype: torch.dtype, layout: str, user_kwargs: dict,
-                   num_sms: int = _policy.NUM_SMS_DEFAULT) -> _policy.Policy:
+                   num_sms: int = _policy.NUM_SMS_DEFAULT, out_dtype: Optional[torch.dtype] = None) -> _policy.Policy:
     """user_kwargs -> Policy. A dict that names no tiling (empty, or control keys only) first consults the tuned
-    JSONL, then the heuristic."""
+    JSONL, then the heuristic. The table and the heuristic are measured with 16-bit outputs; for an fp32 output
+    (`out_dtype`) their pair tiles wider than 256 columns become 256 wide, because that variant's epilogue, which no main
+    loop hides, takes twice as long with fp32 rows."""
+    def for_output(pol: _policy.Policy) -> _policy.Policy:
+        if out_dtype is torch.float32 and pol.cta_group == 2 and pol.tile_n > 256:
+            return dataclasses.replace(pol, tile_n=256, stages=0)
+        return pol
+
     if not any(key in user_kwargs for key in _policy.REFERENCE_KEYS + _policy.BLACKWELL_KEYS):
         rec = _policy.tuned_lookup(_dtype_name(dtype), layout, m, n, k)
         if rec is not None:
             control = {key: val for key, val in user_kwargs.items() if key in _policy.CONTROL_KEYS}
-            pol = _policy.from_user_kwargs({**rec, **control}, m, n, k, layout, num_sms)
+            pol = for_output(_policy.from_user_kwargs({**rec, **control}, m, n, k, layout, num_sms))
             if _policy.validate(pol, m, n, k, layout) is None:  # a row tuned for another layout may not fit this one
                 return pol
-    return _policy.from_user_kwargs(user_kwargs, m, n, k, layout, num_sms)
+    pol = _policy.from_user_kwargs(user_kwargs, m, n, k, layout, num_sms)
+    return pol if "tile_n" in user_kwargs else for_output(pol)
 
 
 def make_gemm_a16w16_param_and_validate(m: int, n: int, k: int, kwargs: dict):
@@ -370,7 +380,7 @@ def gemm_a16w16(
                 out.copy_(bias.to(out.dtype).expand(m, n))
         return out
 
-    pol = resolve_policy(m, n, k, a.dtype, layout, user_kwargs, _num_sms(device))
+    pol = resolve_policy(m, n, k, a.dtype, layout, user_kwargs, _num_sms(device), out_dtype)
     why = _policy.validate(pol, m, n, k, layout)
     assert why is None, f"unsupported gemm_a16w16 shape/config: {why}"
 
@@ -435,7 +445,7 @@ def gemm_a16w16_to_pointer(a: torch.Tensor, b: torch.Tensor, out_ptr: int, out_d
     assert b.shape[0] == k and m > 0 and n > 0 and k > 0
     _check_operand("A", a, a_t, False, m)
     _check_operand("B", b, b_t, False, None)
-    pol = resolve_policy(m, n, k, a.dtype, layout, user_kwargs, _num_sms(device))
+    pol = resolve_policy(m, n, k, a.dtype, layout, user_kwargs, _num_sms(device), out_dtype)
     why = _policy.validate(pol, m, n, k, layout)
     assert why is None, f"unsupported gemm_a16w16 shape/config: {why}"
     args = _fill_args(a, b, torch.empty(0, dtype=out_dtype), None, pol, a_t, b_t)
@@ -468,7 +478,7 @@ def plan(a: torch.Tensor, b: torch.Tensor, layout: str = "nt", user_kwargs: dict
     m, k = a.shape
     n = b.shape[1]
     out_dtype = out_dtype or a.dtype
-    pol = resolve_policy(m, n, k, a.dtype, layout, user_kwargs)
+    pol = resolve_policy(m, n, k, a.dtype, layout, user_kwargs, out_dtype=out_dtype)
     fake_out = torch.empty(0, dtype=out_dtype)
     args = _fill_args(a, b, fake_out, bias, pol, a_t, b_t)
     pl = _lib.Plan()

@@ -245,6 +245,14 @@ def test_tuned_rows_serve_other_layouts_only_when_valid():
     # config 4: the 256x192 pair of the 'nt' row needs a K-contiguous B; 'nn' has its own row
     assert resolve_policy(1000, 3000, 4100, torch.float16, "tt", {}).tile_n == 192
     assert resolve_policy(1000, 3000, 4100, torch.float16, "nn", {}).tile_n == 256
+    # rows and heuristic picks with pair tiles wider than 256 columns are for 16-bit outputs; fp32 outputs get 256
+    wide = resolve_policy(16384, 28672, 8192, torch.bfloat16, "nt", {})
+    assert (wide.tile_n, wide.cta_group, wide.group_m) == (512, 2, 8)
+    narrow = resolve_policy(16384, 28672, 8192, torch.bfloat16, "nt", {}, out_dtype=torch.float32)
+    assert (narrow.tile_n, narrow.cta_group, narrow.group_m) == (256, 2, 8)
+    assert resolve_policy(6000, 6000, 6000, torch.bfloat16, "nt", {}).tile_n == 512
+    assert resolve_policy(6000, 6000, 6000, torch.bfloat16, "nt", {}, out_dtype=torch.float32).tile_n == 256
+    assert resolve_policy(6000, 6000, 6000, torch.bfloat16, "nt", {"tile_n": 480, "cta_group": 2}, out_dtype=torch.float32).tile_n == 480
 
 
 @pytest.mark.parametrize(("tiles", "kb", "cap"), [(256, 64, 148), (96, 65, 148), (3, 112, 148), (1792, 128, 148), (149, 2, 148),
