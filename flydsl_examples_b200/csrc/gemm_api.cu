@@ -85,12 +85,18 @@ static const Variant* find_variant(int tile_q, int cta_group, int tile_k) {
   return nullptr;
 }
 
+// V rows of one CTA as laid out in a stage: whole 64-row boxes once there are more than 64 (96 -> 128)
+static int v_slot_rows(int tile_q, int cta_group) {
+  const int rows = tile_q / cta_group;
+  return rows > 64 ? (rows + 63) / 64 * 64 : rows;
+}
+
 static int dyn_smem_bytes(int tile_q, int stages, int cta_group, int tile_k) {
   const int staging0 = tile_q >= 64 ? 4 * 2 * 32 * 128 : 0;
   const int recv = tile_q <= 64 ? kTileP * tile_q * 4 : 0;
   const int staging = recv > staging0 ? recv : staging0;
   const int bias = tile_q > 256 ? tile_q * 2 : 256 * 4;
-  return stages * (kTileP * tile_k * 2 + (tile_q / cta_group) * tile_k * 2) + staging + bias + (2 * stages + 4) * 8 + 32 + 1024;
+  return stages * (kTileP * tile_k * 2 + v_slot_rows(tile_q, cta_group) * tile_k * 2) + staging + bias + (2 * stages + 4) * 8 + 32 + 1024;
 }
 
 struct DeviceInfo {
@@ -184,8 +190,9 @@ static int resolve(const b200_gemm_args* a, Resolved* r, bool need_sm_count, int
     r->P = (int)a->n, r->Q = (int)a->m;
     r->u_mn = b_mn, r->v_mn = a_mn;
   }
-  // an MN-major operand is fetched in boxes 64 elements wide: each CTA's share of tile_n must be whole boxes
-  if (r->v_mn && (var->tile_q / pl.cta_group) % 64 != 0) return B200_GEMM_ERR_BAD_POLICY;
+  // an MN-major operand is fetched in boxes 64 elements wide: each CTA's share of tile_n must be at least one box (a
+  // share of 96 columns takes two boxes and uses one and a half)
+  if (r->v_mn && var->tile_q / pl.cta_group < 64) return B200_GEMM_ERR_BAD_POLICY;
 
   pl.tiles_p = (r->P + pl.tile_m - 1) / pl.tile_m;
   pl.tiles_q = (r->Q + pl.tile_n - 1) / pl.tile_n;
@@ -421,7 +428,8 @@ static int prepare(const b200_gemm_args* a, b200_gemm_handle* h) {
   p.u_cp = u_cp, p.v_cp = v_cp;
   p.u_src = u_ptr, p.v_src = v_ptr;
   p.u_pitch = u_ld * 2, p.v_pitch = v_ld * 2;
-  p.tma_tx_bytes = (uint32_t)(pl.cta_group * pl.tile_k * 2 * ((u_cp ? 0 : kTileP) + (v_cp ? 0 : pl.tile_n / pl.cta_group)));
+  const int v_tma_rows = r.v_mn ? v_slot_rows(pl.tile_n, pl.cta_group) : pl.tile_n / pl.cta_group;  // whole boxes when MN-major
+  p.tma_tx_bytes = (uint32_t)(pl.cta_group * pl.tile_k * 2 * ((u_cp ? 0 : kTileP) + (v_cp ? 0 : v_tma_rows)));
   p.out = a->out;
   p.bias = a->bias;
   {

@@ -181,7 +181,10 @@ struct SmemLayout {
   // CTA's V rows (half h of the tile = columns 256h .. 256h+255 of the accumulator).
   static constexpr int kHalves = TILE_Q > 256 ? 2 : 1;
   static constexpr int kMmaVRows = kVRows / kHalves;
-  static constexpr int kVBoxBytes = kVRows * kBoxK * 2;
+  // An operand that is contiguous along its rows arrives in boxes of 64 rows: a CTA's share of 96 rows (the 192-wide
+  // pair tile) then occupies two boxes, so the V part of a stage is sized for whole boxes.
+  static constexpr int kVBoxRows = kVRows > 64 ? (kVRows + 63) / 64 * 64 : kVRows;
+  static constexpr int kVBoxBytes = kVBoxRows * kBoxK * 2;
   static constexpr int kUStageBytes = kSub * kUBoxBytes;
   static constexpr int kVStageBytes = kSub * kVBoxBytes;
   static constexpr int kStageBytes = kUStageBytes + kVStageBytes;
@@ -313,7 +316,10 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
   constexpr int kAccBufs = 2 * TILE_Q <= 512 ? 2 : 1;
   constexpr uint32_t kTmemCols = 2 * TILE_Q <= 32 ? 32 : 2 * TILE_Q <= 64 ? 64 : 2 * TILE_Q <= 128 ? 128 : 2 * TILE_Q <= 256 ? 256 : 512;
   // a pair's two CTAs both report to the leader's barrier; with loader warps only the TMA-fetched operand counts
-  const uint32_t tx_bytes = LOADER ? p.tma_tx_bytes : (uint32_t)(CG * L::kStageBytes);
+  // (a K-contiguous V of 96 rows per CTA fills only three quarters of its two-box slot)
+  const uint32_t tx_bytes = LOADER                      ? p.tma_tx_bytes
+                            : L::kVBoxRows != L::kVRows ? (uint32_t)(CG * (L::kUStageBytes + L::kSub * (p.v_mn_major ? L::kVBoxBytes : L::kVRows * kBoxK * 2)))
+                                                        : (uint32_t)(CG * L::kStageBytes);
   // arrivals that complete a stage: the producer's expect_tx, plus one per CTA from its loader warps
   constexpr uint32_t kFullArrivals = LOADER ? 1 + CG : 1;
   constexpr int kVRows = L::kVRows;
@@ -436,9 +442,9 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
 #pragma unroll
             for (int h = 0; h < L::kHalves; ++h) load(bv + (uint32_t)(h * kMmaVRows * 128), &p.tmap_v, k0, half_q0(h), fb);
           } else {
-            constexpr int kPerHalf = kMmaVRows >= 64 ? kMmaVRows / 64 : 1;  // 64-row boxes per accumulator half
+            constexpr int kPerHalf = kMmaVRows >= 64 ? (kMmaVRows + 63) / 64 : 1;  // 64-row boxes per accumulator half
 #pragma unroll
-            for (int j = 0; j < (kVRows >= 64 ? kVRows / 64 : 1); ++j)
+            for (int j = 0; j < (kVRows >= 64 ? (kVRows + 63) / 64 : 1); ++j)
               load(bv + 8192u * j, &p.tmap_v, half_q0(j / kPerHalf) + 64 * (j % kPerHalf), k0, fb);
           }
         }

@@ -87,7 +87,10 @@ def smem_bytes(tile_n: int, stages: int, cta_group: int = 1, requested_tile_k: i
     staging = max(staging, TILE_M * tile_n * 4 if tile_n <= 64 else 0)  # rows received in cluster split-K mode
     tk = tile_k(tile_n, cta_group, requested_tile_k)
     bias = tile_n * 2 if tile_n > 256 else 256 * 4  # a 512-wide tile keeps its bias slice in 16 bits
-    return stages * (TILE_M * tk * 2 + (tile_n // cta_group) * tk * 2) + staging + bias + (2 * stages + 4) * 8 + 32 + 1024
+    v_rows = tile_n // cta_group
+    if v_rows > 64:
+        v_rows = -(-v_rows // 64) * 64  # whole 64-row boxes (the 192-wide pair tile: 96 -> 128)
+    return stages * (TILE_M * tk * 2 + v_rows * tk * 2) + staging + bias + (2 * stages + 4) * 8 + 32 + 1024
 
 
 def split_k_slices(k: int, split_k: int, tk: int = TILE_K) -> list[tuple[int, int]]:
@@ -195,8 +198,8 @@ def validate(pol: Policy, m: int, n: int, k: int, layout: str) -> Optional[str]:
     a_mn = layout[0] == "t"
     b_mn = layout[1] == "n"
     v_mn = a_mn if pol.swap_ab else b_mn
-    if v_mn and (width // pol.cta_group) % 64 != 0:
-        return "a tile_n-side operand that is not K-contiguous needs a multiple of 64 tile_n columns per CTA"
+    if v_mn and width // pol.cta_group < 64:
+        return "a tile_n-side operand that is not K-contiguous needs at least 64 tile_n columns per CTA"
     if pol.tile_n > TMEM_COLUMNS:
         return "the accumulator does not fit in 512 TMEM columns"
     return None
@@ -262,8 +265,7 @@ def heuristic(m: int, n: int, k: int, layout: str = "nt", num_sms: int = NUM_SMS
             cands.append((2, 256))
             if q > 256:
                 cands.append((2, 512))  # a quarter less operand traffic per flop; pays on many-wave problems with long K
-            if not v_mn:
-                cands.append((2, 192))  # 96 columns per CTA: K-contiguous tile_n-side operand only
+            cands.append((2, 192))
         best = min(cands, key=lambda c: (_estimate_cycles(p_ext, q, kb, c[0], c[1], num_sms), -c[1], -c[0]))
         cta_group, tile_n = best
     walkers = num_sms // cta_group

@@ -294,7 +294,7 @@ def test_cta_pair_shapes(dtype, idx):
                      repeats=2, prefill="randn")
 
 
-PAIR_192 = [  # 256 x 192 pair tiles: 96 columns per CTA, so B must be K-contiguous ('nt', 'tt')
+PAIR_192 = [  # 256 x 192 pair tiles: 96 columns per CTA (one and a half 64-row boxes of an N-contiguous B)
     (512, 768, 520, {"tile_n": 192, "cta_group": 2}),
     (700, 500, 1000, {"tile_n": 192, "cta_group": 2}),                      # ragged in M and N
     (1000, 3000, 4100, {"tile_n": 192, "cta_group": 2}),                    # config 4's shape: 64 pair tiles
@@ -308,12 +308,26 @@ PAIR_192 = [  # 256 x 192 pair tiles: 96 columns per CTA, so B must be K-contigu
 @pytest.mark.parametrize("idx", range(len(PAIR_192)))
 def test_cta_pair_192_wide_tiles(dtype, idx):
     m, n, k, kw = PAIR_192[idx]
-    for layout in ("nt", "tt"):
+    for layout in LAYOUTS:
         for out_dtype in (None, "fp32"):
             run_case(O.Case("pair192", dtype, layout, m, n, k, seed=450 + idx, bias_std=0.5, out_dtype=out_dtype, user_kwargs=kw),
                      repeats=2, prefill="randn")
-    with pytest.raises(AssertionError):  # N-contiguous B cannot be cut into 96-column shares
-        run_case(O.Case("pair192", dtype, "nn", m, n, k, seed=1, user_kwargs=kw))
+
+
+def test_cta_pair_192_exact_integers_all_layouts():
+    # small integers: a misplaced box of the one-and-a-half-box V share shows as a wrong integer
+    g = torch.Generator().manual_seed(7)
+    m, n, k = 512, 1000, 1096
+    a_l = torch.randint(-2, 3, (m, k), generator=g).to(torch.float16)
+    b_l = torch.randint(-2, 3, (k, n), generator=g).to(torch.float16)
+    ref = (a_l.double() @ b_l.double()).float()
+    for layout in LAYOUTS:
+        a = O.place(a_l, layout[0] == "t", 0, 0, DEV)
+        b = O.place(b_l, layout[1] == "t", 0, 0, DEV)
+        for kw in ({"tile_n": 192, "cta_group": 2}, {"tile_n": 192, "cta_group": 2, "stages": 3, "stream_k": True}):
+            got = gemm_a16w16(a, b, layout=layout, out_dtype=torch.float32, user_kwargs=kw)
+            check_status()
+            assert torch.equal(got.cpu(), ref), (layout, kw)
 
 
 PAIR_512 = [  # 256 x 512 pair tiles: two MMAs per K step into one accumulator that fills TMEM
