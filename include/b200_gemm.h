@@ -55,10 +55,11 @@ extern "C" {
 /* Blackwell policy. Replaces the reference's compile-time GemmA16W16Gfx950Param
  * (kernels/gemm_a16w16_gfx950.py:33-61): block_m/n/k, stages, split_k, *_waves, group_m, HTI flag. */
 typedef struct b200_gemm_policy {
-  int32_t tile_n;     /* columns of one tile: 16, 32, 64, 128 or 256; also 192 and 512 for CTA pairs (512 = two MMAs per K step
-                         into one accumulator that fills TMEM: a quarter less operand traffic per flop, but the epilogue no
-                         longer overlaps the next tile's main loop). Tile M is 128 per CTA; the K extent of a pipeline
-                         stage follows from the variant, see b200_gemm_describe_variant                            */
+  int32_t tile_n;     /* columns of one tile: 16, 32, 64, 128 or 256; for CTA pairs also 192 and any multiple of 32 from 288 to
+                         512 (one kernel variant, two MMAs per K step into one accumulator that fills TMEM: up to a quarter
+                         less operand traffic per flop, but the epilogue no longer overlaps the next tile's main loop; the
+                         width is a run-time parameter so that the caller can fill whole waves). Tile M is 128 per CTA; the
+                         K extent of a pipeline stage follows from the variant, see b200_gemm_describe_variant      */
   int32_t stages;     /* depth of the TMA->smem ring; 0, or more than fit in 227 KB, = as many as fit              */
   int32_t split_k;    /* >= 1 K-slices per output tile (uneven slices allowed, K tail is zero-filled by TMA)      */
   int32_t group_m;    /* grouped rasterisation: tiles are walked in groups of group_m tile rows; 0 = row-major     */
