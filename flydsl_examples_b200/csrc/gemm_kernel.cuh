@@ -786,10 +786,7 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
         float v[CW];
 #pragma unroll
         for (int i = 0; i < CW; ++i) v[i] = __uint_as_float(r[i]);
-        // an odd number of chunks (512-column variant): the last one has no partner to fill a 128-byte row of 16-bit
-        // output with, and leaves through the direct path
-        const bool lone = TILE_Q > 256 && p.out_dtype != 1 && c == nchunk - 1 && (c & 1) == 0;
-        if (staged && !lone) {
+        if (TILE_Q < 128 && staged) {  // (tiles of 128 columns and more take the 64-column steps below)
           if constexpr (CW == 32) {
             if constexpr (TILE_Q > 256) {
               if (p.bias != nullptr && !red) add_bias16(c, v, 0);
@@ -884,11 +881,12 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
       };
       bool done = false;
       uint32_t ra[32], rb[32];  // two register buffers for tcgen05.ld
-      if constexpr (TILE_Q > 256) {
-        // The single accumulator of this variant leaves its epilogue unhidden, so the common exit (whole tile, 16-bit
-        // output, TMA stores) takes 64 columns per step in one straight-line block: two tcgen05.ld, one wait, bias,
-        // cast, the lane's 128-byte row segment into the warp's swizzled staging image, one flush. The loads of the
-        // next step are issued once this step's values have left the registers and fly during the flush.
+      if constexpr (CW == 32 && TILE_Q >= 128) {
+        // The common exit (whole tile, 16-bit output, TMA stores) takes 64 columns per step in one straight-line
+        // block: two tcgen05.ld, one wait, bias, cast, the lane's 128-byte row segment into the warp's swizzled
+        // staging image, one flush. The loads of the next step are issued once this step's values have left the
+        // registers and fly during the flush. (The 512-column variant needs it most: its single accumulator leaves
+        // every epilogue unhidden.)
         if (staged && !red && p.out_dtype != 1) {
           done = true;
           const int nstep = nchunk >> 1;
@@ -905,7 +903,18 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
               float v[32];
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-              if (p.bias != nullptr) add_bias16(2 * sp + h, v, 0);
+              if (p.bias != nullptr) {
+                if constexpr (TILE_Q > 256) {
+                  add_bias16(2 * sp + h, v, 0);
+                } else {
+                  const float4* b4 = reinterpret_cast<const float4*>(bias_s + sp * 64 + h * 32);  // 16-byte aligned
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    const float4 b = b4[j];
+                    v[4 * j] += b.x, v[4 * j + 1] += b.y, v[4 * j + 2] += b.z, v[4 * j + 3] += b.w;
+                  }
+                }
+              }
               if (p.out_dtype == 2) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
@@ -946,6 +955,62 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
 #pragma unroll
             for (int i = 0; i < CW; ++i) v[i] = __uint_as_float(ra[i]);
             finalize(v, nchunk - 1);
+          }
+        } else if (staged) {
+          // fp32 rows (whole tiles, and the partial tiles of the atomic mode): the same steps, one 32-column image
+          // and one flush per half
+          done = true;
+          const int nstep = nchunk >> 1;
+          const bool lone = (nchunk & 1) != 0;
+          auto half32 = [&](uint32_t(&r)[32], int c) {  // chunk c: bias, the lane's 128-byte row segment, flush
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            if (p.bias != nullptr && !red) {  // in the atomic mode C already holds the bias
+              if constexpr (TILE_Q > 256) {
+                add_bias16(c, v, 0);
+              } else {
+                const float4* b4 = reinterpret_cast<const float4*>(bias_s + c * CW);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float4 b = b4[j];
+                  v[4 * j] += b.x, v[4 * j + 1] += b.y, v[4 * j + 2] += b.z, v[4 * j + 3] += b.w;
+                }
+              }
+            }
+            stage_acquire();
+            const uint32_t row_base = stage_image() + (uint32_t)lane * 128u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t addr = row_base + (uint32_t)((j ^ (lane & 7)) << 4);
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]),
+                           "f"(v[4 * j + 3])
+                           : "memory");
+            }
+          };
+          load_chunk(ra, 0);
+          load_chunk(rb, 1);
+#pragma unroll 1
+          for (int sp = 0; sp < nstep; ++sp) {
+            tmem_ld_wait();
+            const bool more = sp + 1 < nstep;
+            if (!more && !lone) release_acc();
+            half32(ra, 2 * sp);
+            stage_flush(qbase + sp * 64);
+            half32(rb, 2 * sp + 1);
+            if (more) {
+              load_chunk(ra, 2 * sp + 2);
+              load_chunk(rb, 2 * sp + 3);
+            } else if (lone) {
+              load_chunk(ra, nchunk - 1);
+            }
+            stage_flush(qbase + sp * 64 + 32);
+          }
+          if (lone) {
+            tmem_ld_wait();
+            release_acc();
+            half32(ra, nchunk - 1);
+            stage_flush(qbase + (nchunk - 1) * CW);
           }
         }
       }

@@ -41,7 +41,12 @@ def test_shipped_tuned_row(rec):
     other = "fp16" if rec["dtype"] == "bf16" else "bf16"
     for dt_name, layout in ((rec["dtype"], rec["layout"]), (other, "nn")):
         dtype = DT[dt_name]
-        want = P.from_user_kwargs(cfg, m, n, k, layout)
+        # the row itself for its own (dtype, layout); for the other combination whichever row the lookup prefers
+        # (one of the same layout, if the table has it)
+        looked = P.tuned_lookup(dt_name, layout, m, n, k)
+        if (dt_name, layout) == (rec["dtype"], rec["layout"]):
+            assert looked == cfg
+        want = P.from_user_kwargs(looked, m, n, k, layout)
         got_pol = G.resolve_policy(m, n, k, dtype, layout, {})
         if P.validate(want, m, n, k, layout) is None:
             assert got_pol == want, f"the default call did not pick the shipped row: {got_pol} != {want}"
