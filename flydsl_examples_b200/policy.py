@@ -215,6 +215,15 @@ _KBLOCK_CYCLES = {(1, 256): 800.0, (2, 256): 590.0, (2, 512): 1060.0, (2, 192): 
 _FIXED_CYCLES = 6000.0  # launch tail, pipeline fill, last epilogue
 
 
+def _kblock_cycles(cta_group: int, tile_n: int) -> float:
+    if cta_group == 2 and tile_n > 256:
+        # the 512-column variant at a run-time width: per K = 16 step one MMA of 256 columns (128 cycles) and one of
+        # tile_n - 256, which cannot be issued in less than about 90 cycles however narrow it is (measured: 288 to 416
+        # columns all take about 900 cycles per K block, 512 columns 1060)
+        return 4.0 * (128.0 + max(90.0, (tile_n - 256) / 2.0)) + 36.0
+    return _KBLOCK_CYCLES[(cta_group, tile_n)]
+
+
 def _auto_split(tiles: int, kb: int, walkers: int, cluster_ok: bool = False) -> tuple[int, str]:
     """(K slices per tile, reduction mode) when the tiles alone cannot occupy the machine. Narrow single-CTA tiles
     reduce inside a thread-block cluster (2..16 CTAs, through distributed shared memory); the rest use tickets."""
@@ -235,14 +244,14 @@ def _estimate_cycles(p_ext: int, q: int, kb: int, cta_group: int, tile_n: int, n
     split, _ = _auto_split(tiles, kb, walkers, cta_group == 1 and tile_n <= 64)
     waves = -(-(tiles * split) // walkers)
     # per tile, outside the main loop: the hand-over between tiles; a 512-wide tile has a single accumulator, so its
-    # whole epilogue (about 8 us) stands between two main loops
-    epilogue = 12000.0 if tile_n > 256 else 1000.0 + 500.0 * tile_n / 256
+    # whole epilogue (5 to 6 us at 512 columns) stands between two main loops
+    epilogue = 9000.0 * tile_n / 512 if tile_n > 256 else 1000.0 + 500.0 * tile_n / 256
     # after the main loop: a cluster exchange of a narrow tile costs about 1 us, a reduction through global memory
     # (partial write, fences and ticket, read-back) about 5 us
     # (the last arriver reads split slabs of 128 x tile_n floats at about 24 bytes per clock)
     fixup = 0.0 if split <= 1 else (1500.0 + 200.0 * split) if (cta_group == 1 and tile_n <= 64) else (8000.0 + 21.0 * split * tile_n)
     pair_start = 2500.0 if cta_group == 2 else 0.0  # a cluster launch reaches its first MMA about 1.5 us later
-    return _FIXED_CYCLES + pair_start + waves * (-(-kb // split) * _KBLOCK_CYCLES[(cta_group, tile_n)] + epilogue) + fixup
+    return _FIXED_CYCLES + pair_start + waves * (-(-kb // split) * _kblock_cycles(cta_group, tile_n) + epilogue) + fixup
 
 
 def heuristic(m: int, n: int, k: int, layout: str = "nt", num_sms: int = NUM_SMS_DEFAULT) -> Policy:
@@ -264,7 +273,9 @@ def heuristic(m: int, n: int, k: int, layout: str = "nt", num_sms: int = NUM_SMS
         if p_ext > TILE_M and q > 128:
             cands.append((2, 256))
             if q > 256:
-                cands.append((2, 512))  # a quarter less operand traffic per flop; pays on many-wave problems with long K
+                # the 512-column variant at the widths that may fill whole waves better: up to a quarter less operand
+                # traffic per flop, but an epilogue that no main loop hides
+                cands += [(2, t) for t in range(288, 513, 32)]
             cands.append((2, 192))
         best = min(cands, key=lambda c: (_estimate_cycles(p_ext, q, kb, c[0], c[1], num_sms), -c[1], -c[0]))
         cta_group, tile_n = best
