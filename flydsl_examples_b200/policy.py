@@ -301,7 +301,7 @@ def from_user_kwargs(user_kwargs: dict, m: int, n: int, k: int, layout: str, num
     if native:
         # A Blackwell policy is taken literally: nothing the caller left out is second-guessed by the heuristic
         # except the tile, which falls back to the heuristic's choice.
-        fields.update(split_k=1, group_m=0, swap_ab=False, stages=0, cta_group=1, split_mode="ticket")
+        fields.update(split_k=1, group_m=0, swap_ab=False, stages=0, cta_group=1, split_mode="ticket", tile_k=0)
         for key in BLACKWELL_KEYS + ("stages", "split_k", "group_m"):
             if key in user_kwargs:
                 fields[key] = user_kwargs[key]
