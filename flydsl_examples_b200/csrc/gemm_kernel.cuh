@@ -880,7 +880,9 @@ __global__ void __launch_bounds__(LOADER ? kThreadsLoader : kThreads, 1) gemm_a1
         }
       };
       bool done = false;
-      uint32_t ra[32], rb[32];  // two register buffers for tcgen05.ld
+      // Two register buffers for tcgen05.ld, declared once for all the loops below: with buffers of their own per
+      // loop the compiler spilled values that the producer's and the MMA issuer's loops use (config 5: +20 %).
+      uint32_t ra[32], rb[32];
       if constexpr (CW == 32 && TILE_Q >= 128) {
         // The common exit (whole tile, 16-bit output, TMA stores) takes 64 columns per step in one straight-line
         // block: two tcgen05.ld, one wait, bias, cast, the lane's 128-byte row segment into the warp's swizzled
