@@ -387,6 +387,22 @@ def test_pair_512_other_exits(width):
         assert torch.equal(got.cpu(), ref), (layout, kw)
 
 
+@pytest.mark.parametrize("shape", [(1536, 4096, 4096), (2304, 2304, 8192), (5000, 3000, 8000), (3000, 5000, 2000)])
+def test_heuristic_run_time_widths_through_the_default_path(shape):
+    # shapes outside the shipped table for which the heuristic picks a run-time width of the 512-column variant
+    m, n, k = shape
+    a = (torch.randn(m, k, device=DEV) * 0.05).to(torch.bfloat16)
+    b = (torch.randn(n, k, device=DEV) * 0.05).to(torch.bfloat16).t()
+    bias = torch.randn(n, device=DEV).to(torch.bfloat16)
+    pl = plan(a, b, "nt", {}, bias=bias)
+    assert pl["cta_group"] == 2 and 256 < pl["tile_n"] <= 512 and pl["tile_n"] % 32 == 0, pl
+    out = gemm_a16w16(a, b, bias=bias, layout="nt")
+    check_status()
+    sampled_check(out, a.cpu(), b.cpu(), bias.cpu(), k, torch.bfloat16, n_rows=24, n_cols=24, seed=m)
+    # an fp32 output of the same problem falls back to 256-wide pair tiles
+    assert plan(a, b, "nt", {}, out_dtype=torch.float32, bias=bias)["tile_n"] == 256
+
+
 def test_pair_512_plan():
     a = torch.empty(2048, 4096, dtype=torch.bfloat16, device=DEV)
     b = torch.empty(4096, 4096, dtype=torch.bfloat16, device=DEV).t()

@@ -137,6 +137,25 @@ def test_heuristic_is_always_valid():
             assert P.validate(pol, m, n, k, layout) is None, (m, n, k, layout, pol)
 
 
+def test_heuristic_is_valid_on_random_shapes():
+    import random
+
+    rng = random.Random(1234)
+    seen_wide = 0
+    for _ in range(400):
+        m = rng.choice([1, 7, 33, 130, 300, 700, 1536, 2304, 5000, 9000, rng.randint(1, 12000)])
+        n = rng.choice([16, 100, 384, 2000, 4096, 5120, 7000, rng.randint(8, 30000)])
+        k = rng.choice([64, 200, 1000, 4100, 8192, rng.randint(1, 16384)])
+        layout = rng.choice(["nn", "nt", "tn", "tt"])
+        pol = P.heuristic(m, n, k, layout)
+        assert P.validate(pol, m, n, k, layout) is None, (m, n, k, layout, pol)
+        if pol.cta_group == 2 and pol.tile_n > 256:
+            seen_wide += 1
+            assert pol.tile_n % 32 == 0 and pol.tile_n <= 512
+            assert P.smem_bytes(pol.tile_n, P.max_stages(pol.tile_n, 2), 2) <= P.SMEM_LIMIT
+    assert seen_wide > 0  # the run-time widths of the 512-column variant are among the picks
+
+
 def test_split_k_slices_cover_k_exactly_once():
     for k, tk in ((1, 64), (63, 64), (64, 128), (65, 64), (1000, 128), (4100, 64), (4100, 128), (7168, 128)):
         for s in (1, 2, 3, 7, 8, 16, 32, 200):
